@@ -1,0 +1,139 @@
+/*
+ * rdq_b200.h -- C ABI of the B200 (sm_100a) mixed-precision linear operator.
+ *
+ * One shared library (librdq_b200.so) exports these entry points.  Every
+ * pointer is a plain device pointer unless stated otherwise; no torch types
+ * cross this boundary.  All entry points
+ *   - launch on the CUDA stream handed in (a cudaStream_t passed as void*,
+ *     NULL = legacy default stream) of the CURRENT device,
+ *   - return 0 on success and a negative RDQ_E_* code on failure, with a
+ *     human readable message available from rdq_last_error() (thread local),
+ *   - keep no global state; the only cross-launch state is the caller-owned
+ *     `counters` array of the stream GEMV, which must be zero on first use and
+ *     is returned to zero by every launch that completes.
+ *
+ * Tensor layouts are the packed-checkpoint layouts of the reference
+ * (rdquant/integrations/hf_export.py:58-125), rows in permuted
+ * (format-grouped) channel order NVFP4 | FP8 | FP16:
+ *   w_fp4         u8  [n_fp4, K/2]   byte = (code[2j+1] << 4) | code[2j]
+ *   w_fp4_scales  u8  [n_fp4, K/16]  E4M3 bits, one per 16 consecutive k
+ *   w_fp8         u8  [n_fp8, K]     E4M3 bits
+ *   w_fp8_scales  f32 [n_fp8]        one scale per channel
+ *   w_fp16        f16 [n_fp16, K]    (bf16 accepted by rdq_dequant_packed)
+ *   inv_perm      i32 [N]            y[j] = y_perm[inv_perm[j]]
+ *   perm          i32 [N]            perm[inv_perm[j]] = j ; permuted row p is
+ *                                    original channel perm[p]
+ * Dequantised value of an NVFP4 element is LUT[code] * e4m3(block scale); the
+ * `w_fp4_global_scale` argument multiplies that (reference kernels do the
+ * same, rdquant/csrc/fused_gemv.cu:673-674).  Checkpoints written by
+ * quantize_model store absolute block scales, so their callers pass 1.0
+ * (rdquant/core/formats.py:145-159 ignores the stored global scale).
+ */
+#ifndef RDQ_B200_H_
+#define RDQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RDQ_OK               0
+#define RDQ_E_INVALID       -1  /* bad shape / alignment / null pointer        */
+#define RDQ_E_UNSUPPORTED   -2  /* shape outside what the kernel family takes */
+#define RDQ_E_CUDA          -3  /* a CUDA runtime call failed                 */
+#define RDQ_E_DEVICE        -4  /* kernel reported a bounded wait ran out     */
+
+#define RDQ_MAX_GEMV_M      16  /* decode GEMV accepts 1..16 activation rows  */
+
+/* Library / build identification. */
+int         rdq_version(void);
+const char *rdq_last_error(void);
+
+/*
+ * Bit-exact dequantisation of one packed layer to FP16 [N, K] in ORIGINAL
+ * channel order.  Replaces rdquant/inference.py:67-121
+ * (_materialize_packed_groups) followed by cat()[inv_perm]
+ * (rdquant/inference.py:828-841) and equals
+ * QuantizedWeight.dequantize().half() (rdquant/quantize.py:50-69).
+ * NVFP4: f16(LUT[code] * e4m3(scale) * global); FP8: f16(f32(e4m3) * scale);
+ * FP16 group copied (fp16_is_bf16 != 0: bf16 -> f32 -> f16, round to nearest).
+ * out_is_f32 != 0 writes FP32 [N, K] holding the unrounded FP32 products, which
+ * is what rdquant.core.formats.dequantize returns (rdquant/core/formats.py:385-395).
+ * inv_perm == NULL means identity.  K % 16 == 0 when n_fp4 > 0.
+ */
+int rdq_dequant_packed(const void *w_fp4, const void *w_fp4_scales,
+                       float w_fp4_global_scale,
+                       const void *w_fp8, const float *w_fp8_scales,
+                       const void *w_fp16, int fp16_is_bf16,
+                       const int32_t *inv_perm,
+                       void *w_out, int out_is_f32,
+                       int n_fp4, int n_fp8, int n_fp16, int K,
+                       void *stream);
+
+/*
+ * Scratch the stream GEMV needs for a layer of N output channels on the
+ * current device: `*workspace_bytes` of float scratch (contents irrelevant)
+ * and `*counter_bytes` of int32 counters (must start zeroed).
+ */
+int rdq_gemv_scratch_size(int N, size_t *workspace_bytes, size_t *counter_bytes);
+
+/*
+ * Decode GEMV, M <= 16:  y[m, perm[p]] = sum_k x[m,k] * W_perm[p,k] (+ bias).
+ * One launch covers the NVFP4, FP8 and FP16 groups and scatters to original
+ * channel order.  Replaces fused_mixed_gemv and the split-K family
+ * (rdquant/csrc/rdquant_ops.h:75-85, :104-234; launchers
+ * rdquant/csrc/fused_gemv.cu:2049-2393) and, together with the FP16 group,
+ * the cat + index_select tail of rdquant/ops.py:60-66.
+ *   x     f16 [M, K] row-major (ldx = K)
+ *   y     f16 [M, N] row-major, every element written
+ *   bias  f16 [N] in original channel order, or NULL
+ *   workspace / counters: from rdq_gemv_scratch_size; may both be NULL, in
+ *     which case only the self-contained kernel (no K split) is used.
+ *   flags: RDQ_GEMV_* below.
+ * FP32 accumulation; NVFP4 weights enter the product as f16(LUT*scale)
+ * (exact), FP8 weights as f16(e4m3) with the channel scale applied to the
+ * FP32 sum.  Deterministic: repeated calls give identical bits.
+ */
+#define RDQ_GEMV_AUTO        0   /* pick stream kernel when the shape allows */
+#define RDQ_GEMV_GENERIC     1   /* force the any-shape kernel               */
+#define RDQ_GEMV_STREAM      2   /* force the TMA-staged stream kernel       */
+#define RDQ_GEMV_PDL         16  /* launch with programmatic dependent launch:
+                                    weights are prefetched before the wait on
+                                    the preceding kernel, x is read after it */
+int rdq_gemv_mixed(const void *x, int M,
+                   const void *w_fp4, const void *w_fp4_scales,
+                   float w_fp4_global_scale,
+                   const void *w_fp8, const float *w_fp8_scales,
+                   const void *w_fp16,
+                   const int32_t *perm, const void *bias,
+                   void *y,
+                   int n_fp4, int n_fp8, int n_fp16, int K,
+                   void *workspace, int32_t *counters,
+                   int flags, void *stream);
+
+/*
+ * Prefill GEMM, any M >= 1 (meant for M >= 16):
+ *   y[m, j] = sum_k x[m,k] * W[j,k] (+ bias[j]),  j in original channel order.
+ * Weight tiles are gathered by inv_perm, dequantised to FP16 into shared
+ * memory and multiplied by tcgen05 kind::f16 MMAs with FP32 accumulators in
+ * tensor memory.  Replaces the dense-prefill F.linear over a materialised
+ * FP16 copy (rdquant/inference.py:679-687) and the 2x marlin_gemm + cat +
+ * index_select path (rdquant/inference.py:620-677).
+ *   x f16 [M, K], y f16 [M, N]; K % 64 == 0; inv_perm NULL = identity.
+ */
+int rdq_gemm_mixed(const void *x, int M,
+                   const void *w_fp4, const void *w_fp4_scales,
+                   float w_fp4_global_scale,
+                   const void *w_fp8, const float *w_fp8_scales,
+                   const void *w_fp16,
+                   const int32_t *inv_perm, const void *bias,
+                   void *y,
+                   int n_fp4, int n_fp8, int n_fp16, int K,
+                   void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RDQ_B200_H_ */

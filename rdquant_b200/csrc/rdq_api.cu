@@ -1,0 +1,158 @@
+// C ABI of librdq_b200.so: argument validation and dispatch to the kernels.
+// Declarations and the reference interfaces they replace: include/rdq_b200.h.
+#include <cstdarg>
+#include <cstring>
+
+#include "rdq_kernels.cuh"
+
+namespace rdq {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 1;
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+  if (dev >= 0 && dev < 64) cached[dev] = n;
+  return n;
+}
+
+namespace {
+
+// Shape / pointer checks shared by the three operators; mirrors the
+// TORCH_CHECKs of the reference wrapper (rdquant/csrc/bindings.cpp:167-182).
+int check_layer(const void *w_fp4, const void *w_fp4_scales, const void *w_fp8,
+                const float *w_fp8_scales, const void *w_fp16, int n4, int n8, int n16, int K) {
+  RDQ_REQUIRE(n4 >= 0 && n8 >= 0 && n16 >= 0, RDQ_E_INVALID, "group sizes must be non-negative");
+  RDQ_REQUIRE(K > 0, RDQ_E_INVALID, "K must be positive");
+  if (n4 > 0) {
+    RDQ_REQUIRE(K % 16 == 0, RDQ_E_INVALID,
+                "NVFP4 group needs K to be a multiple of 16 (one E4M3 scale per 16 k), got K=%d", K);
+    RDQ_REQUIRE(w_fp4 && w_fp4_scales, RDQ_E_INVALID, "w_fp4 / w_fp4_scales must not be null when n_fp4 > 0");
+    RDQ_REQUIRE(aligned16(w_fp4) && aligned16(w_fp4_scales), RDQ_E_INVALID,
+                "w_fp4 / w_fp4_scales must be 16-byte aligned");
+  }
+  if (n8 > 0) {
+    RDQ_REQUIRE(w_fp8 && w_fp8_scales, RDQ_E_INVALID, "w_fp8 / w_fp8_scales must not be null when n_fp8 > 0");
+    RDQ_REQUIRE(aligned16(w_fp8), RDQ_E_INVALID, "w_fp8 must be 16-byte aligned");
+  }
+  if (n16 > 0) {
+    RDQ_REQUIRE(w_fp16 != nullptr, RDQ_E_INVALID, "w_fp16 must not be null when n_fp16 > 0");
+    RDQ_REQUIRE(aligned16(w_fp16), RDQ_E_INVALID, "w_fp16 must be 16-byte aligned");
+  }
+  return RDQ_OK;
+}
+
+}  // namespace
+}  // namespace rdq
+
+using namespace rdq;
+
+extern "C" {
+
+int rdq_version(void) { return 100; }
+
+const char *rdq_last_error(void) { return g_error; }
+
+int rdq_dequant_packed(const void *w_fp4, const void *w_fp4_scales, float w_fp4_global_scale,
+                       const void *w_fp8, const float *w_fp8_scales, const void *w_fp16,
+                       int fp16_is_bf16, const int32_t *inv_perm, void *w_out, int out_is_f32,
+                       int n_fp4, int n_fp8, int n_fp16, int K, void *stream) {
+  int rc = check_layer(w_fp4, w_fp4_scales, w_fp8, w_fp8_scales, w_fp16, n_fp4, n_fp8, n_fp16, K);
+  if (rc != RDQ_OK) return rc;
+  if (n_fp4 + n_fp8 + n_fp16 == 0) return RDQ_OK;
+  RDQ_REQUIRE(w_out != nullptr && aligned16(w_out), RDQ_E_INVALID, "w_out must be a 16-byte aligned device pointer");
+  return launch_dequant(w_fp4, w_fp4_scales, w_fp4_global_scale, w_fp8, w_fp8_scales, w_fp16,
+                        fp16_is_bf16, inv_perm, w_out, out_is_f32, n_fp4, n_fp8, n_fp16, K,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int rdq_gemv_scratch_size(int N, size_t *workspace_bytes, size_t *counter_bytes) {
+  RDQ_REQUIRE(N >= 0 && workspace_bytes && counter_bytes, RDQ_E_INVALID, "bad arguments to rdq_gemv_scratch_size");
+  gemv_stream_scratch(N, workspace_bytes, counter_bytes);
+  return RDQ_OK;
+}
+
+int rdq_gemv_mixed(const void *x, int M, const void *w_fp4, const void *w_fp4_scales,
+                   float w_fp4_global_scale, const void *w_fp8, const float *w_fp8_scales,
+                   const void *w_fp16, const int32_t *perm, const void *bias, void *y, int n_fp4,
+                   int n_fp8, int n_fp16, int K, void *workspace, int32_t *counters, int flags,
+                   void *stream) {
+  int rc = check_layer(w_fp4, w_fp4_scales, w_fp8, w_fp8_scales, w_fp16, n_fp4, n_fp8, n_fp16, K);
+  if (rc != RDQ_OK) return rc;
+  RDQ_REQUIRE(M >= 0 && M <= RDQ_MAX_GEMV_M, RDQ_E_UNSUPPORTED,
+              "rdq_gemv_mixed takes 1..%d activation rows, got M=%d (use rdq_gemm_mixed)", RDQ_MAX_GEMV_M, M);
+  if (M == 0 || n_fp4 + n_fp8 + n_fp16 == 0) return RDQ_OK;
+  RDQ_REQUIRE(x != nullptr && y != nullptr, RDQ_E_INVALID, "x and y must not be null");
+  RDQ_REQUIRE(aligned16(x) || (K % 16 != 0), RDQ_E_INVALID, "x must be 16-byte aligned");
+  GemvArgs a;
+  a.x = static_cast<const __half *>(x);
+  a.M = M;
+  a.w4 = static_cast<const uint8_t *>(w_fp4);
+  a.s4 = static_cast<const uint8_t *>(w_fp4_scales);
+  a.global4 = w_fp4_global_scale;
+  a.w8 = static_cast<const uint8_t *>(w_fp8);
+  a.s8 = w_fp8_scales;
+  a.w16 = static_cast<const __half *>(w_fp16);
+  a.perm = perm;
+  a.bias = static_cast<const __half *>(bias);
+  a.y = static_cast<__half *>(y);
+  a.n4 = n_fp4;
+  a.n8 = n_fp8;
+  a.n16 = n_fp16;
+  a.K = K;
+  a.workspace = static_cast<float *>(workspace);
+  a.counters = counters;
+  const int mode = flags & 15;
+  const bool pdl = (flags & RDQ_GEMV_PDL) != 0;
+  const bool can_stream = gemv_stream_supported(a);
+  if (mode == RDQ_GEMV_STREAM) {
+    RDQ_REQUIRE(can_stream, RDQ_E_UNSUPPORTED,
+                "stream GEMV needs K %% 256 == 0, groups in multiples of 16 rows and scratch buffers "
+                "(K=%d, n=%d/%d/%d)", K, n_fp4, n_fp8, n_fp16);
+  }
+  if (mode != RDQ_GEMV_GENERIC && can_stream) return launch_gemv_stream(a, pdl, static_cast<cudaStream_t>(stream));
+  return launch_gemv_generic(a, static_cast<cudaStream_t>(stream));
+}
+
+int rdq_gemm_mixed(const void *x, int M, const void *w_fp4, const void *w_fp4_scales,
+                   float w_fp4_global_scale, const void *w_fp8, const float *w_fp8_scales,
+                   const void *w_fp16, const int32_t *inv_perm, const void *bias, void *y, int n_fp4,
+                   int n_fp8, int n_fp16, int K, void *stream) {
+  int rc = check_layer(w_fp4, w_fp4_scales, w_fp8, w_fp8_scales, w_fp16, n_fp4, n_fp8, n_fp16, K);
+  if (rc != RDQ_OK) return rc;
+  RDQ_REQUIRE(M >= 0, RDQ_E_INVALID, "M must be non-negative");
+  if (M == 0 || n_fp4 + n_fp8 + n_fp16 == 0) return RDQ_OK;
+  RDQ_REQUIRE(x != nullptr && y != nullptr, RDQ_E_INVALID, "x and y must not be null");
+  RDQ_REQUIRE(aligned16(x) && aligned16(y), RDQ_E_INVALID, "x and y must be 16-byte aligned");
+  RDQ_REQUIRE(K % 64 == 0, RDQ_E_UNSUPPORTED, "rdq_gemm_mixed needs K to be a multiple of 64, got K=%d", K);
+  GemmArgs a;
+  a.x = static_cast<const __half *>(x);
+  a.M = M;
+  a.w4 = static_cast<const uint8_t *>(w_fp4);
+  a.s4 = static_cast<const uint8_t *>(w_fp4_scales);
+  a.global4 = w_fp4_global_scale;
+  a.w8 = static_cast<const uint8_t *>(w_fp8);
+  a.s8 = w_fp8_scales;
+  a.w16 = static_cast<const __half *>(w_fp16);
+  a.inv_perm = inv_perm;
+  a.bias = static_cast<const __half *>(bias);
+  a.y = static_cast<__half *>(y);
+  a.n4 = n_fp4;
+  a.n8 = n_fp8;
+  a.n16 = n_fp16;
+  a.K = K;
+  return launch_gemm(a, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,57 @@
+// Internal launch interfaces shared by the C-ABI translation unit and the
+// kernel translation units.
+#pragma once
+
+#include "rdq_common.cuh"
+
+namespace rdq {
+
+// Arguments of the decode GEMV kernels (permuted-row tensors, see rdq_b200.h).
+struct GemvArgs {
+  const __half *x;
+  int M;
+  const uint8_t *w4;
+  const uint8_t *s4;
+  float global4;
+  const uint8_t *w8;
+  const float *s8;
+  const __half *w16;
+  const int32_t *perm;
+  const __half *bias;
+  __half *y;
+  int n4, n8, n16, K;
+  float *workspace;   // stream kernel: per-CTA partial-tile slots
+  int32_t *counters;  // stream kernel: per-tile arrival counters + status word
+};
+
+struct GemmArgs {
+  const __half *x;
+  int M;
+  const uint8_t *w4;
+  const uint8_t *s4;
+  float global4;
+  const uint8_t *w8;
+  const float *s8;
+  const __half *w16;
+  const int32_t *inv_perm;
+  const __half *bias;
+  __half *y;
+  int n4, n8, n16, K;
+};
+
+int launch_dequant(const void *w_fp4, const void *w_fp4_scales, float global4, const void *w_fp8,
+                   const float *w_fp8_scales, const void *w_fp16, int fp16_is_bf16,
+                   const int32_t *inv_perm, void *w_out, int out_is_f32, int n4, int n8, int n16,
+                   int K, cudaStream_t stream);
+
+int launch_gemv_generic(const GemvArgs &a, cudaStream_t stream);
+
+// True when the TMA-staged stream kernel accepts the shape / pointers.
+bool gemv_stream_supported(const GemvArgs &a);
+int launch_gemv_stream(const GemvArgs &a, bool pdl, cudaStream_t stream);
+// workspace floats / counter ints the stream kernel needs for N output rows
+void gemv_stream_scratch(int N, size_t *workspace_bytes, size_t *counter_bytes);
+
+int launch_gemm(const GemmArgs &a, cudaStream_t stream);
+
+}  // namespace rdq

@@ -1,0 +1,218 @@
+"""Inference modules over the fused kernels (reference: rdquant/inference.py).
+
+``FusedMixedLinear`` keeps the constructor and attributes of the reference module
+(rdquant/inference.py:408-512) and ``load_for_inference`` its signature (:715-722).  Both
+decode (M <= 16, one GEMV launch) and prefill (tcgen05 GEMM) run from the packed tensors;
+no dequantised FP16 copy of the weights is kept, so ``use_dense_prefill`` costs no memory.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from rdquant_b200 import _lib
+from rdquant_b200.fused_gemv_pack import (
+    build_marlin_data,
+    fused_gemv_available,
+    get_rdquant_cuda,
+    pack_for_fused_gemv,
+)
+
+_FD_TENSORS = ("w_fp4_q", "w_fp4_scales", "w_fp8_q", "w_fp8_scales", "w_fp16", "perm", "inv_perm",
+               "workspace", "tile_counters")
+
+
+def _normalize_torch_dtype(dtype_like) -> torch.dtype:
+    if isinstance(dtype_like, torch.dtype):
+        return dtype_like
+    table = {"float16": torch.float16, "half": torch.float16, "bfloat16": torch.bfloat16,
+             "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+    if isinstance(dtype_like, str):
+        return table.get(dtype_like.lower(), torch.bfloat16)
+    return torch.bfloat16
+
+
+def _materialize_packed_groups(layer_data: dict, splits: dict, n_in: int) -> dict:
+    """Dequantised FP16 groups in permuted order (rdquant/inference.py:67-121), computed by
+    the dequantisation kernel; tensors must already be on a CUDA device."""
+    cuda = get_rdquant_cuda()
+    out = {"w_nvfp4": None, "w_fp8": None, "w_fp16": None}
+    for fmt, key in (("NVFP4", "w_nvfp4"), ("FP8", "w_fp8"), ("FP16", "w_fp16")):
+        if int(splits.get(fmt, 0)) > 0:
+            only = {f: (int(splits[f]) if f == fmt else 0) for f in ("NVFP4", "FP8", "FP16")}
+            out[key] = cuda.dequantize_packed(layer_data, only, n_in, inv_perm=None)
+    return out
+
+
+class FusedMixedLinear(nn.Module):
+    """Packed mixed-precision linear: fused GEMV for decode, tcgen05 GEMM for prefill."""
+
+    def __init__(
+        self,
+        *,
+        n_nvfp4: int,
+        n_fp8: int,
+        n_fp16: int,
+        k: int,
+        inv_perm: torch.Tensor,
+        bias: Optional[torch.Tensor],
+        marlin_data: Optional[dict] = None,
+        fused_data: Optional[dict] = None,
+        w_fp16_fp16: Optional[torch.Tensor] = None,
+        w_prefill_fp16: Optional[torch.Tensor] = None,
+    ) -> None:
+        super().__init__()
+        self.n_nvfp4, self.n_fp8, self.n_fp16 = int(n_nvfp4), int(n_fp8), int(n_fp16)
+        self.N = self.n_nvfp4 + self.n_fp8 + self.n_fp16
+        self.K = int(k)
+        self.register_buffer("inv_perm", inv_perm.to(torch.int64))
+        self.register_buffer("_inv_perm_i32", inv_perm.to(torch.int32))
+        self.bias = nn.Parameter(bias.clone()) if bias is not None else None
+        # marlin_data / w_fp16_fp16 / w_prefill_fp16 belong to the reference's fallback paths
+        # and are accepted but unused: every shape runs from the packed buffers.
+        self._has_marlin = False
+        self._has_fused = fused_data is not None
+        self.use_pdl = False
+        self._fd_scalars = {}
+        if fused_data is not None:
+            if (fused_data["n_fp4"], fused_data["n_fp8"], fused_data["n_fp16"], fused_data["k"]) != (
+                    self.n_nvfp4, self.n_fp8, self.n_fp16, self.K):
+                raise ValueError("fused_data does not match the layer's group sizes / K")
+            for name in _FD_TENSORS:
+                t = fused_data.get(name)
+                if t is not None:
+                    self.register_buffer(f"_fused_{name}", t, persistent=False)
+            self._fd_scalars = {kk: v for kk, v in fused_data.items() if kk not in _FD_TENSORS}
+        self._fd_cache = None
+        self._bias_h = None
+
+    def _apply(self, fn, recurse=True):
+        self._fd_cache = None
+        self._bias_h = None
+        return super()._apply(fn, recurse)
+
+    def _fd(self) -> dict:
+        if self._fd_cache is None:
+            fd = dict(self._fd_scalars)
+            for name in _FD_TENSORS:
+                fd[name] = getattr(self, f"_fused_{name}", None)
+            self._fd_cache = fd
+        return self._fd_cache
+
+    def _can_use_fused(self, x_2d: torch.Tensor) -> bool:
+        return self._has_fused and x_2d.is_cuda
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        orig_shape = x.shape
+        x_2d = x.reshape(-1, self.K)
+        if not self._can_use_fused(x_2d):
+            raise RuntimeError("No compatible fused backend available (needs CUDA tensors and packed buffers)")
+        cuda = get_rdquant_cuda()
+        x_half = x_2d if x_2d.dtype == torch.float16 else x_2d.half()
+        x_half = x_half.contiguous()
+        bias_h = None
+        if self.bias is not None:
+            if self._bias_h is None or self._bias_h.device != x.device:
+                self._bias_h = self.bias.detach().to(device=x.device, dtype=torch.float16).contiguous()
+            bias_h = self._bias_h
+        flags = _lib.RDQ_GEMV_PDL if self.use_pdl else 0
+        y = cuda.mixed_linear(x_half, self._fd(), bias_h, flags)
+        return y.to(x.dtype).reshape(*orig_shape[:-1], self.N)
+
+    def extra_repr(self) -> str:
+        return f"K={self.K}, N={self.N}, nvfp4/fp8/fp16={self.n_nvfp4}/{self.n_fp8}/{self.n_fp16}"
+
+    @classmethod
+    def from_layer_data(cls, layer_data: dict, splits: dict, k: int, device) -> "FusedMixedLinear":
+        fd = pack_for_fused_gemv(layer_data, dict(splits), k, device)
+        if fd is None:
+            raise RuntimeError("rdquant_b200 kernels unavailable: build librdq_b200.so and run on a CUDA device")
+        bias = layer_data.get("bias")
+        return cls(n_nvfp4=fd["n_fp4"], n_fp8=fd["n_fp8"], n_fp16=fd["n_fp16"], k=k,
+                   inv_perm=fd["inv_perm"], bias=bias.to(device) if bias is not None else None,
+                   marlin_data=None, fused_data=fd)
+
+
+# The grouped two-launch module of the reference (rdquant/inference.py:144-391) has the same
+# contract; one class serves both names.
+MarlinMixedLinear = FusedMixedLinear
+
+
+def _set_module(model: nn.Module, name: str, new_module: nn.Module) -> None:
+    parts = name.split(".")
+    parent = model
+    for part in parts[:-1]:
+        parent = getattr(parent, part)
+    setattr(parent, parts[-1], new_module)
+
+
+def replace_quantized_layers(model: nn.Module, layer_configs: dict, tensors: dict, device) -> None:
+    """Install a :class:`FusedMixedLinear` for every layer of ``layer_configs``."""
+    for layer_name, lconf in layer_configs.items():
+        pre = layer_name + "."
+        layer_data = {k[len(pre):]: v for k, v in tensors.items() if k.startswith(pre)}
+        mod = FusedMixedLinear.from_layer_data(layer_data, lconf["splits"], lconf["in_features"], device)
+        _set_module(model, layer_name, mod)
+
+
+def load_for_inference(
+    checkpoint_dir: str,
+    model_class=None,
+    device: str = "cuda",
+    use_marlin: bool = True,
+    use_fused_gemv: bool = True,
+    use_dense_prefill: bool = True,
+) -> nn.Module:
+    """Load a packed checkpoint into a HuggingFace model whose quantised linears are
+    :class:`FusedMixedLinear`.
+
+    ``use_marlin`` / ``use_fused_gemv`` / ``use_dense_prefill`` are accepted for signature
+    parity (rdquant/inference.py:715-722); the fused kernels serve decode and prefill alike.
+    """
+    from safetensors import safe_open
+    from transformers import AutoConfig, AutoModelForCausalLM
+
+    target = torch.device(device)
+    if target.type != "cuda" or not fused_gemv_available():
+        raise RuntimeError("load_for_inference needs a CUDA device and the built rdquant_b200 kernels")
+    if model_class is None:
+        model_class = AutoModelForCausalLM
+
+    with open(os.path.join(checkpoint_dir, "quantization_config.json")) as fh:
+        qconfig = json.load(fh)
+    layer_configs = qconfig["layers"]
+
+    config = AutoConfig.from_pretrained(checkpoint_dir)
+    model_dtype = _normalize_torch_dtype(getattr(config, "torch_dtype", None) or getattr(config, "dtype", torch.bfloat16))
+    with torch.device("meta"):
+        model = model_class.from_config(config)
+    model = model.to_empty(device="cpu")
+    model.eval()
+
+    tensors: dict[str, torch.Tensor] = {}
+    with safe_open(os.path.join(checkpoint_dir, "model.safetensors"), framework="pt", device="cpu") as fh:
+        for key in fh.keys():
+            tensors[key] = fh.get_tensor(key)
+
+    replace_quantized_layers(model, layer_configs, tensors, target)
+
+    quant_layers = tuple(name + "." for name in layer_configs)
+    for pname, param in model.named_parameters():
+        if not pname.startswith(quant_layers) and pname in tensors:
+            param.data.copy_(tensors[pname].to(param.dtype))
+    for bname, buf in model.named_buffers():
+        if not bname.startswith(quant_layers) and bname in tensors:
+            buf.copy_(tensors[bname].to(buf.dtype))
+
+    if getattr(config, "tie_word_embeddings", False):
+        if hasattr(model, "lm_head") and hasattr(model, "model") and hasattr(model.model, "embed_tokens"):
+            model.lm_head.weight = model.model.embed_tokens.weight
+
+    model = model.to(device)
+    model.eval()
+    del model_dtype
+    return model

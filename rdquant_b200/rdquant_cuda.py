@@ -1,0 +1,223 @@
+"""Torch-facing wrappers over the C ABI of ``librdq_b200.so``.
+
+Plays the role of the reference's pybind extension module ``rdquant_cuda``
+(rdquant/csrc/bindings.cpp:979-990): validate tensors, allocate the output with torch,
+hand raw device pointers and the current CUDA stream to the C entry points.  Failures
+surface as ``RuntimeError`` like the reference's ``TORCH_CHECK``s.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from rdquant_b200 import _lib
+
+MAX_GEMV_M = 16
+GEMM_READY = False
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(device: torch.device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _need_cuda(name: str, t: Optional[torch.Tensor], dtype=None) -> None:
+    if t is None:
+        return
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+class _on_device:
+    """Make ``device`` current for the duration of a call (the C ABI uses the current device)."""
+
+    def __init__(self, device: torch.device) -> None:
+        self.idx = device.index if device.index is not None else torch.cuda.current_device()
+        self.prev = None
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+
+
+def perm_from_inv_perm(inv_perm: torch.Tensor) -> torch.Tensor:
+    """int32 ``perm`` with ``perm[inv_perm[j]] = j``: permuted row p is original channel perm[p]
+    (rdquant/core/allocator.py:222-224, rdquant/integrations/hf_export.py:243-245)."""
+    inv = inv_perm.to(torch.int64)
+    perm = torch.empty_like(inv)
+    perm[inv] = torch.arange(inv.numel(), dtype=torch.int64, device=inv.device)
+    return perm.to(torch.int32)
+
+
+def gemv_scratch(n_out: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """(workspace, tile_counters) for the stream GEMV of a layer with ``n_out`` channels."""
+    device = torch.device(device)
+    ws, cnt = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    with _on_device(device):
+        _lib.check(_lib.lib().rdq_gemv_scratch_size(int(n_out), ctypes.byref(ws), ctypes.byref(cnt)),
+                   "rdq_gemv_scratch_size")
+    workspace = torch.empty(max(ws.value // 4, 1), dtype=torch.float32, device=device)
+    counters = torch.zeros(max(cnt.value // 4, 1), dtype=torch.int32, device=device)
+    return workspace, counters
+
+
+def dequantize_packed(layer_data: dict, splits: dict, k: int, inv_perm: Optional[torch.Tensor] = None,
+                      out_dtype: torch.dtype = torch.float16, global_scale: float = 1.0) -> torch.Tensor:
+    """Dequantise packed checkpoint tensors to ``[N, K]`` in original channel order.
+
+    ``layer_data`` uses the checkpoint key names (``weight_nvfp4`` ...); ``weight_fp16`` may be
+    bfloat16 (as stored on disk) or float16.  ``out_dtype`` float16 gives the operator's weight,
+    float32 the unrounded products of ``formats.dequantize``.
+    """
+    n4, n8, n16 = (int(splits.get(f, 0)) for f in ("NVFP4", "FP8", "FP16"))
+    w4 = layer_data.get("weight_nvfp4") if n4 else None
+    s4 = layer_data.get("weight_nvfp4_scale") if n4 else None
+    w8 = layer_data.get("weight_fp8") if n8 else None
+    s8 = layer_data.get("weight_fp8_scale") if n8 else None
+    w16 = layer_data.get("weight_fp16") if n16 else None
+    some = next(t for t in (w4, w8, w16) if t is not None)
+    device = some.device
+    _need_cuda("weight_nvfp4", w4, torch.uint8)
+    _need_cuda("weight_nvfp4_scale", s4, torch.uint8)
+    _need_cuda("weight_fp8", w8, torch.uint8)
+    _need_cuda("weight_fp8_scale", s8, torch.float32)
+    _need_cuda("weight_fp16", w16)
+    if w4 is not None and (tuple(w4.shape) != (n4, k // 2) or tuple(s4.shape) != (n4, k // 16)):
+        raise RuntimeError("weight_nvfp4 must be [n4, K/2] and weight_nvfp4_scale [n4, K/16]")
+    if w8 is not None and (tuple(w8.shape) != (n8, k) or s8.numel() != n8):
+        raise RuntimeError("weight_fp8 must be [n8, K] and weight_fp8_scale [n8]")
+    is_bf16 = 0
+    if w16 is not None:
+        if tuple(w16.shape) != (n16, k):
+            raise RuntimeError("weight_fp16 must be [n16, K]")
+        if w16.dtype == torch.bfloat16:
+            is_bf16 = 1
+        elif w16.dtype != torch.float16:
+            raise RuntimeError("weight_fp16 must be float16 or bfloat16")
+    if out_dtype not in (torch.float16, torch.float32):
+        raise RuntimeError("out_dtype must be float16 or float32")
+    inv32 = None
+    if inv_perm is not None:
+        inv32 = inv_perm.to(device=device, dtype=torch.int32).contiguous()
+        if inv32.numel() != n4 + n8 + n16:
+            raise RuntimeError("inv_perm must have N elements")
+    out = torch.empty(n4 + n8 + n16, k, dtype=out_dtype, device=device)
+    with _on_device(device):
+        rc = _lib.lib().rdq_dequant_packed(_ptr(w4), _ptr(s4), float(global_scale), _ptr(w8), _ptr(s8), _ptr(w16),
+                                           is_bf16, _ptr(inv32), _ptr(out), int(out_dtype == torch.float32),
+                                           n4, n8, n16, int(k), _stream(device))
+    _lib.check(rc, "rdq_dequant_packed")
+    return out
+
+
+def mixed_gemv(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None, flags: int = 0,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``y[M, N] = x[M, K] @ W.T (+ bias)`` for M <= 16 from a ``pack_for_fused_gemv`` dict."""
+    _need_cuda("x", x, torch.float16)
+    if x.dim() != 2:
+        raise RuntimeError("x must be 2-D [M, K]")
+    m, k = x.shape
+    if k != fd["k"]:
+        raise RuntimeError(f"x.size(1)={k} must match K={fd['k']}")
+    if m > MAX_GEMV_M:
+        raise RuntimeError(f"decode GEMV takes at most {MAX_GEMV_M} rows, got {m}")
+    n4, n8, n16 = fd["n_fp4"], fd["n_fp8"], fd["n_fp16"]
+    n = n4 + n8 + n16
+    if bias is not None:
+        _need_cuda("bias", bias, torch.float16)
+        if bias.numel() != n:
+            raise RuntimeError("bias must have N elements")
+    y = out if out is not None else torch.empty(m, n, dtype=torch.float16, device=x.device)
+    with _on_device(x.device):
+        rc = _lib.lib().rdq_gemv_mixed(
+            _ptr(x), m, _ptr(fd.get("w_fp4_q")), _ptr(fd.get("w_fp4_scales")), float(fd.get("w_fp4_global_scale", 1.0)),
+            _ptr(fd.get("w_fp8_q")), _ptr(fd.get("w_fp8_scales")), _ptr(fd.get("w_fp16")), _ptr(fd.get("perm")),
+            _ptr(bias), _ptr(y), n4, n8, n16, k, _ptr(fd.get("workspace")), _ptr(fd.get("tile_counters")),
+            int(flags), _stream(x.device))
+    _lib.check(rc, "rdq_gemv_mixed")
+    return y
+
+
+def mixed_gemm(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Prefill GEMM ``y[M, N] = x[M, K] @ W.T (+ bias)`` on the tcgen05 path."""
+    _need_cuda("x", x, torch.float16)
+    if x.dim() != 2:
+        raise RuntimeError("x must be 2-D [M, K]")
+    m, k = x.shape
+    if k != fd["k"]:
+        raise RuntimeError(f"x.size(1)={k} must match K={fd['k']}")
+    n4, n8, n16 = fd["n_fp4"], fd["n_fp8"], fd["n_fp16"]
+    n = n4 + n8 + n16
+    if bias is not None:
+        _need_cuda("bias", bias, torch.float16)
+    y = torch.empty(m, n, dtype=torch.float16, device=x.device)
+    with _on_device(x.device):
+        rc = _lib.lib().rdq_gemm_mixed(
+            _ptr(x), m, _ptr(fd.get("w_fp4_q")), _ptr(fd.get("w_fp4_scales")), float(fd.get("w_fp4_global_scale", 1.0)),
+            _ptr(fd.get("w_fp8_q")), _ptr(fd.get("w_fp8_scales")), _ptr(fd.get("w_fp16")), _ptr(fd.get("inv_perm")),
+            _ptr(bias), _ptr(y), n4, n8, n16, k, _stream(x.device))
+    _lib.check(rc, "rdq_gemm_mixed")
+    return y
+
+
+def mixed_linear(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None, flags: int = 0) -> torch.Tensor:
+    """GEMV for M <= 16, GEMM above."""
+    if x.shape[0] <= MAX_GEMV_M:
+        return mixed_gemv(x, fd, bias, flags)
+    if GEMM_READY:
+        return mixed_gemm(x, fd, bias)
+    # until the tensor-core GEMM is enabled: the decode kernel over 16-row panels
+    n = fd["n_fp4"] + fd["n_fp8"] + fd["n_fp16"]
+    y = torch.empty(x.shape[0], n, dtype=torch.float16, device=x.device)
+    for r0 in range(0, x.shape[0], MAX_GEMV_M):
+        mixed_gemv(x[r0:r0 + MAX_GEMV_M], fd, bias, flags, out=y[r0:r0 + MAX_GEMV_M])
+    return y
+
+
+def fused_mixed_gemv(x: torch.Tensor, w_fp4: torch.Tensor, w_fp4_scales: torch.Tensor, w_fp4_global_scale: float,
+                     w_fp8: torch.Tensor, w_fp8_scales: torch.Tensor, inv_perm: torch.Tensor,
+                     N_fp4: int, N_fp8: int, K: int) -> torch.Tensor:
+    """Signature of the reference's ``rdquant_cuda.fused_mixed_gemv``
+    (rdquant/csrc/bindings.cpp:156-201) on row-major checkpoint tensors, for M <= 16.
+
+    Output placement follows the operator's definition ``y[j] = y_perm[inv_perm[j]]``
+    (rdquant/ops.py:62-63).
+    """
+    for name, t in (("w_fp4", w_fp4), ("w_fp4_scales", w_fp4_scales), ("w_fp8", w_fp8)):
+        _need_cuda(name, t, torch.uint8)
+    _need_cuda("w_fp8_scales", w_fp8_scales, torch.float32)
+    _need_cuda("inv_perm", inv_perm)
+    if x.dim() != 2 or x.size(1) != K:
+        raise RuntimeError("x must be [M, K]")
+    if w_fp4.size(0) != N_fp4 or w_fp8.size(0) != N_fp8:
+        raise RuntimeError("weight rows must match N_fp4/N_fp8")
+    if N_fp4 and (w_fp4.size(1) * 2 != K or tuple(w_fp4_scales.shape) != (N_fp4, K // 16)):
+        raise RuntimeError("w_fp4 must be [N_fp4, K/2] and w_fp4_scales [N_fp4, K/16]")
+    if N_fp8 and (w_fp8.size(1) != K or w_fp8_scales.numel() != N_fp8):
+        raise RuntimeError("w_fp8 must be [N_fp8, K] and w_fp8_scales [N_fp8]")
+    if inv_perm.numel() != N_fp4 + N_fp8:
+        raise RuntimeError("inv_perm must have N_fp4 + N_fp8 elements")
+    ws, cnt = gemv_scratch(N_fp4 + N_fp8, x.device)
+    fd = {
+        "w_fp4_q": w_fp4 if N_fp4 else None, "w_fp4_scales": w_fp4_scales if N_fp4 else None,
+        "w_fp4_global_scale": float(w_fp4_global_scale),
+        "w_fp8_q": w_fp8 if N_fp8 else None, "w_fp8_scales": w_fp8_scales if N_fp8 else None,
+        "w_fp16": None, "perm": perm_from_inv_perm(inv_perm), "workspace": ws, "tile_counters": cnt,
+        "n_fp4": int(N_fp4), "n_fp8": int(N_fp8), "n_fp16": 0, "k": int(K),
+    }
+    return mixed_gemv(x, fd)

@@ -1,0 +1,93 @@
+"""Decode GEMV (M <= 16) through the C ABI against the oracle: golden layers, random byte
+patterns, the benchmark shapes, both kernels, bias, determinism."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import ORDER, golden_layer_torch
+from oracle import oracle_np as onp
+from rdquant_b200 import _lib, rdquant_cuda
+from rdquant_b200.fused_gemv_pack import pack_for_fused_gemv
+from rdquant_b200.synthetic import QWEN3_4B_BLOCK, fixed_splits, random_packed_layer
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3  # max |y - y_ref| / max |y_ref|, FP32-accumulation reference
+
+
+def _run(layer, splits, k, m, flags, bias=False, seed=0):
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randn(m, k, generator=gen).half()
+    n = sum(splits.values())
+    b = (torch.randn(n, generator=gen) * 0.5).half() if bias else None
+    fd = pack_for_fused_gemv(layer, splits, k, "cuda")
+    y = rdquant_cuda.mixed_gemv(x.cuda(), fd, b.cuda() if bias else None, flags)
+    torch.cuda.synchronize()
+    y_ref = onp.mixed_precision_linear(x.numpy(), onp.torch_layer_to_np(layer), splits, k,
+                                       b.float().numpy() if bias else None)
+    cnt = fd["tile_counters"].cpu()
+    assert int(cnt.abs().sum()) == 0, "tile counters / status word not back to zero"
+    return y.cpu().float().numpy(), y_ref, fd
+
+
+@pytest.mark.parametrize("flags", [_lib.RDQ_GEMV_GENERIC, _lib.RDQ_GEMV_AUTO])
+def test_golden_layers(layers, flags):
+    for name, case in layers.items():
+        layer, splits, k = golden_layer_torch(case)
+        for m in (1, 3):
+            y, y_ref, _ = _run(layer, splits, k, m, flags, bias="bias" in layer)
+            assert onp.rel_err(y, y_ref) < TOL, (name, m)
+
+
+@pytest.mark.parametrize("m", [1, 2, 4, 8, 9, 16])
+@pytest.mark.parametrize("shape", [(128, 128, 128, 256), (64, 32, 16, 512), (256, 0, 0, 1024), (0, 48, 0, 256),
+                                   (0, 0, 32, 768), (1664, 768, 128, 4096)])
+@pytest.mark.parametrize("flags", [_lib.RDQ_GEMV_GENERIC, _lib.RDQ_GEMV_STREAM])
+def test_random_bytes(shape, m, flags):
+    n4, n8, n16, k = shape
+    layer = random_packed_layer(n4, n8, n16, k, seed=k + m)
+    splits = dict(zip(ORDER, (n4, n8, n16)))
+    y, y_ref, _ = _run(layer, splits, k, m, flags, bias=(m % 2 == 0), seed=m)
+    assert onp.rel_err(y, y_ref) < TOL
+
+
+def test_ragged_shapes_take_generic_kernel():
+    for n4, n8, n16, k in [(49, 46, 1, 64), (0, 33, 7, 40), (5, 0, 0, 16)]:
+        layer = random_packed_layer(n4, n8, n16, k, seed=7)
+        splits = dict(zip(ORDER, (n4, n8, n16)))
+        y, y_ref, _ = _run(layer, splits, k, 3, _lib.RDQ_GEMV_AUTO)
+        assert onp.rel_err(y, y_ref) < TOL
+        with pytest.raises(RuntimeError):
+            _run(layer, splits, k, 1, _lib.RDQ_GEMV_STREAM)
+
+
+@pytest.mark.parametrize("name", list(QWEN3_4B_BLOCK))
+@pytest.mark.parametrize("m", [1, 4, 16])
+def test_block_shapes_random_perm(name, m):
+    k, n = QWEN3_4B_BLOCK[name]
+    splits = fixed_splits(n)
+    layer = random_packed_layer(splits["NVFP4"], splits["FP8"], splits["FP16"], k, seed=len(name) + m)
+    y, y_ref, fd = _run(layer, splits, k, m, _lib.RDQ_GEMV_STREAM | _lib.RDQ_GEMV_PDL, bias=True, seed=m)
+    assert onp.rel_err(y, y_ref) < TOL, (name, m)
+    # determinism: same bits on a second launch
+    gen = torch.Generator().manual_seed(m)
+    x = torch.randn(m, k, generator=gen).half().cuda()
+    y1 = rdquant_cuda.mixed_gemv(x, fd)
+    y2 = rdquant_cuda.mixed_gemv(x, fd)
+    assert torch.equal(y1, y2)
+    # linearity in x (size-independent property): f(2x) == 2 f(x) exactly in float16 unless overflow
+    y3 = rdquant_cuda.mixed_gemv((x * 2).contiguous(), fd)
+    assert torch.allclose(y3.float(), 2 * y1.float(), rtol=2e-3, atol=1e-3)
+
+
+def test_reference_signature_entry_point():
+    n4, n8, k = 128, 64, 256
+    layer = random_packed_layer(n4, n8, 0, k, seed=3)
+    dev = {kk: v.cuda() for kk, v in layer.items()}
+    x = torch.randn(1, k).half()
+    y = rdquant_cuda.fused_mixed_gemv(x.cuda(), dev["weight_nvfp4"], dev["weight_nvfp4_scale"], 1.0, dev["weight_fp8"],
+                                      dev["weight_fp8_scale"], dev["inv_permutation"], n4, n8, k)
+    y_ref = onp.mixed_precision_linear(x.numpy(), onp.torch_layer_to_np(layer), {"NVFP4": n4, "FP8": n8, "FP16": 0}, k)
+    assert y.shape == (1, n4 + n8) and onp.rel_err(y.cpu().float().numpy(), y_ref) < TOL
+    with pytest.raises(RuntimeError):
+        rdquant_cuda.fused_mixed_gemv(x.cuda().float(), dev["weight_nvfp4"], dev["weight_nvfp4_scale"], 1.0,
+                                      dev["weight_fp8"], dev["weight_fp8_scale"], dev["inv_permutation"], n4, n8, k)
