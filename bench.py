@@ -186,6 +186,7 @@ def main() -> None:
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel", default="stream", choices=["stream", "generic"])
+    ap.add_argument("--no-l2-prefetch", action="store_true")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -216,6 +217,8 @@ def main() -> None:
     flags = (_lib.RDQ_GEMV_STREAM if args.kernel == "stream" else _lib.RDQ_GEMV_GENERIC)
     if not args.no_pdl:
         flags |= _lib.RDQ_GEMV_PDL
+    if args.no_l2_prefetch:
+        flags |= _lib.RDQ_GEMV_NO_L2_PREFETCH
 
     gen = torch.Generator().manual_seed(1234 + rank)
     xs = [torch.randn(m, l["k"], generator=gen).half().to(device) for l in layers]

@@ -102,6 +102,7 @@ int rdq_gemv_scratch_size(int N, size_t *workspace_bytes, size_t *counter_bytes)
 #define RDQ_GEMV_PDL         16  /* launch with programmatic dependent launch:
                                     weights are prefetched before the wait on
                                     the preceding kernel, x is read after it */
+#define RDQ_GEMV_NO_L2_PREFETCH 32 /* stream kernel: skip the bulk L2 prefetch */
 int rdq_gemv_mixed(const void *x, int M,
                    const void *w_fp4, const void *w_fp4_scales,
                    float w_fp4_global_scale,

@@ -32,6 +32,7 @@ RDQ_GEMV_AUTO = 0
 RDQ_GEMV_GENERIC = 1
 RDQ_GEMV_STREAM = 2
 RDQ_GEMV_PDL = 16
+RDQ_GEMV_NO_L2_PREFETCH = 32
 
 _lock = threading.Lock()
 _lib = None

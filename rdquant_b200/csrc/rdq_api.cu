@@ -121,7 +121,8 @@ int rdq_gemv_mixed(const void *x, int M, const void *w_fp4, const void *w_fp4_sc
                 "stream GEMV needs K %% 256 == 0, groups in multiples of 16 rows and scratch buffers "
                 "(K=%d, n=%d/%d/%d)", K, n_fp4, n_fp8, n_fp16);
   }
-  if (mode != RDQ_GEMV_GENERIC && can_stream) return launch_gemv_stream(a, pdl, static_cast<cudaStream_t>(stream));
+  if (mode != RDQ_GEMV_GENERIC && can_stream)
+    return launch_gemv_stream(a, pdl, (flags & RDQ_GEMV_NO_L2_PREFETCH) == 0, static_cast<cudaStream_t>(stream));
   return launch_gemv_generic(a, static_cast<cudaStream_t>(stream));
 }
 

@@ -1,4 +1,4 @@
-// Decode GEMV (M <= 16), TMA-staged stream kernel for sm_100a.
+// Decode GEMV (M <= 16), stream kernel for sm_100a.
 //
 // One launch streams the NVFP4, FP8 and FP16 row groups of a layer exactly once
 // from HBM.  The work is cut into "slices" of 16 permuted rows x 256 k; slices
@@ -7,25 +7,31 @@
 // range of them (slice weights 9 : 16 : 32 = bytes of a 16x256 slice incl.
 // block scales, in units of 256 B).  Inside a CTA:
 //
-//   producer warp   cp.async.bulk (TMA, non-tensor) of up to 512 B per row per
-//                   stage into a 9-stage shared-memory ring, mbarrier tracked;
-//                   starts BEFORE griddepcontrol.wait, so under programmatic
-//                   dependent launch the weights of this layer stream in while
-//                   the preceding kernel is still running.
-//   8 MMA warps     ldmatrix the packed bytes, convert with the hardware
-//                   E2M1 / E4M3 -> f16 converters, scale NVFP4 by the block
-//                   scale (exact in f16), and multiply with x on the tensor
-//                   cores (mma.sync m16n8k16, weights as the 16-row operand,
-//                   the M <= 8 activation rows as the 8-column operand, FP32
-//                   accumulators).  Warps split the k range of a stage.
-//   tile flush      per 16-row tile the 8 partial accumulators are summed
-//                   through shared memory in a fixed order; FP8 channel scale
-//                   and bias are applied and y[m, perm[row]] is stored.
+//   L2 prefetch     before griddepcontrol.wait the CTA asks the TMA unit to pull
+//                   its whole byte range into L2 (cp.async.bulk.prefetch.L2), so
+//                   under programmatic dependent launch the weights of this
+//                   layer stream from HBM while the preceding kernel still runs.
+//   8 MMA warps     the k range of each 16-row tile segment is cut into batches
+//                   (16 rows x 512/256/128 k = 4 KB of weights); batches go round
+//                   robin to the warps.  A lane loads 64 contiguous bytes of row
+//                   g and of row g+8 straight into registers in the order the
+//                   tensor-core fragment wants (the k order inside a batch is
+//                   permuted identically for x), converts with the hardware
+//                   E2M1 / E4M3 -> f16 converters, scales NVFP4 by its block
+//                   scale (exact in f16) and issues mma.sync m16n8k16: weights
+//                   are the 16-row operand, the activation rows the 8-column
+//                   operand, accumulation in FP32.
+//   epilogue warp   per tile segment the 8 partial accumulators are summed in a
+//                   fixed order through a 4-deep shared-memory ring; FP8 channel
+//                   scale and bias are applied and y[m, perm[row]] is stored.
 //
-// A tile whose slices are split between CTAs is finished by the last CTA to
-// arrive (per-tile counter), which sums the per-CTA partials from the scratch
-// workspace in CTA order, so results are bitwise reproducible.  Every wait is
-// bounded; a wait that runs out sets the status word and the kernel drains.
+// A tile whose slices are split between CTAs is finished by the CTA that holds
+// its first slice: the other CTAs publish their partial sums to the scratch
+// workspace and raise a flag, the owner waits for the flags (bounded), sums the
+// partials in CTA order (bitwise reproducible) and lowers the flags again.  A
+// CTA works on its split tiles first so that this hand-over overlaps the rest
+// of its stream.  Every wait is bounded; a wait that runs out sets the status
+// word.
 //
 // Algorithmic traffic per launch: n4*(K/2 + K/16) + n8*(K + 4) + n16*2K bytes.
 //
@@ -40,20 +46,15 @@ namespace {
 
 constexpr int kTileRows = 16;
 constexpr int kSliceK = 256;
-constexpr int kRowPitch = 528;    // 512 B of payload + 16 B skew: conflict-free ldmatrix
-constexpr int kScalePitch = 80;   // 64 B of block scales + 16 B skew
-constexpr int kStageW = kTileRows * kRowPitch;                // 8448
-constexpr int kStageBytes = kStageW + kTileRows * kScalePitch;  // 9728
-constexpr int kStages = 9;
 constexpr int kMmaWarps = 8;
 constexpr int kThreads = (kMmaWarps + 1) * 32;
-constexpr int kRedFloats = kMmaWarps * kTileRows * 16;  // one flush buffer: [warp][row][m]
-constexpr int kSmemBytes = kStages * kStageBytes + 2 * kRedFloats * 4;  // 87552 + 16384
+constexpr int kMetaSegs = 32;                          // segments whose output metadata is staged in smem
 constexpr int kUnit4 = 9, kUnit8 = 16, kUnit16 = 32;
 
 // Static description of the slice schedule; identical on every CTA.
 struct Sched {
   int S;            // slices per tile (K / 256)
+  int t4, t8;       // tiles in the NVFP4 / FP8 groups
   int e4, e8, e16;  // end of the NVFP4 / FP8 / FP16 slice ranges (global slice numbering)
   long long w4, w8, W;  // cumulative weights
   int G;
@@ -83,68 +84,247 @@ struct Sched {
   }
 };
 
-struct Stage {
-  int fmt;    // 0 NVFP4, 1 FP8, 2 FP16
-  int tile;   // tile index inside the format group
-  int gtile;  // tile index over all groups
-  int sl;     // first slice inside the tile
-  int n;      // slices in this stage
+// The part of one 16-row tile that this CTA streams.
+struct Seg {
+  int fmt;     // 0 NVFP4, 1 FP8, 2 FP16
+  int gtile;   // tile index over all groups
+  int row0;    // first row inside the format group
+  int k0, k1;  // element range along k
+  int nb;      // batches (512 / 256 / 128 k each)
+  bool starts, ends;  // covers the first / last slice of its tile
+  bool complete;
 };
 
-__device__ __forceinline__ Stage stage_at(const Sched &sc, int s, int s_end) {
-  Stage st;
-  int local, cap;
-  if (s < sc.e4) {
-    st.fmt = 0; local = s; cap = 4;
-  } else if (s < sc.e8) {
-    st.fmt = 1; local = s - sc.e4; cap = 2;
+__device__ __forceinline__ Seg seg_at(const Sched &sc, int s_begin, int s_end, int gtile) {
+  Seg sg;
+  const int ts = gtile * sc.S;
+  const int a = max(s_begin, ts), b = min(s_end, ts + sc.S);
+  sg.gtile = gtile;
+  sg.k0 = (a - ts) * kSliceK;
+  sg.k1 = (b - ts) * kSliceK;
+  sg.starts = (a == ts);
+  sg.ends = (b == ts + sc.S);
+  sg.complete = sg.starts && sg.ends;
+  if (ts < sc.e4) {
+    sg.fmt = 0; sg.row0 = gtile * kTileRows;
+  } else if (ts < sc.e8) {
+    sg.fmt = 1; sg.row0 = (gtile - sc.t4) * kTileRows;
   } else {
-    st.fmt = 2; local = s - sc.e8; cap = 1;
+    sg.fmt = 2; sg.row0 = (gtile - sc.t4 - sc.t8) * kTileRows;
   }
-  st.tile = local / sc.S;
-  st.sl = local - st.tile * sc.S;
-  st.gtile = s / sc.S;
-  int n = sc.S - st.sl;
-  if (n > cap) n = cap;
-  if (n > s_end - s) n = s_end - s;
-  st.n = n;
-  return st;
+  const int bk = 512 >> sg.fmt;
+  sg.nb = (sg.k1 - sg.k0 + bk - 1) / bk;
+  return sg;
+}
+// processing order of a CTA's segments: the (possibly split) first tile, whose partial
+// another CTA is waiting for, then the (possibly split) last tile, which this CTA
+// finishes, then the whole tiles in between
+__device__ __forceinline__ int seg_order(int q, int nseg) {
+  if (q == 0) return 0;
+  if (q == 1) return nseg - 1;
+  return q - 1;
+}
+__device__ __forceinline__ void st_release_gpu(int32_t *p, int32_t v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int32_t ld_acquire_gpu(const int32_t *p) {
+  int32_t v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
 }
 
-__device__ __forceinline__ uint4 ld_x16(const __half *p) {
+__device__ __forceinline__ uint4 ldg_stream(const void *p) {
   uint4 v;
-  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+  asm volatile("ld.global.nc.L1::evict_first.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "l"(p));
   return v;
 }
-__device__ __forceinline__ uint2 ld_x8(const __half *p) {
+__device__ __forceinline__ uint2 ldg_stream8(const void *p) {
   uint2 v;
-  asm volatile("ld.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  asm volatile("ld.global.nc.L1::evict_first.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
   return v;
 }
-__device__ __forceinline__ uint32_t ld_x4(const __half *p) {
-  uint32_t v;
-  asm volatile("ld.global.u32 %0, [%1];" : "=r"(v) : "l"(p));
+// x is written by the preceding kernel: plain (coherent) loads, issued after the PDL wait
+__device__ __forceinline__ uint4 ld_x16(const __half *p) {
+  uint4 v;
+  asm volatile("ld.global.L1::evict_last.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
   return v;
 }
 __device__ __forceinline__ float ld_cg_f32(const float *p) {
   float v;
-  asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ void l2_prefetch(const void *p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
 
-__device__ __forceinline__ void consumer_bar() {
-  asm volatile("bar.sync 1, %0;" ::"n"(kMmaWarps * 32) : "memory");
+#ifdef RDQ_TIMELINE
+__device__ long long g_timeline[148 * 32];
+__device__ __forceinline__ void tl_mark(int slot) {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  if (blockIdx.x < 148 && slot < 32) g_timeline[blockIdx.x * 32 + slot] = t;
+}
+#define TL_MARK(slot) do { if ((threadIdx.x & 31) == 0) tl_mark(slot); } while (0)
+#else
+#define TL_MARK(slot) do { } while (0)
+#endif
+
+template <int NT>
+struct XRows {
+  const __half *row[NT];
+  bool valid[NT];
+};
+
+// ---- one batch of NVFP4: 16 rows x 512 k; this lane owns k_t .. k_t+127 of rows g, g+8
+template <int NT>
+__device__ __forceinline__ void batch_fp4(float (&acc)[NT][2][4], const GemvArgs &a, const XRows<NT> &xr,
+                                          int row, int k_t, bool tv) {
+  const int K = a.K;
+  uint4 wg[4], wh[4];
+  uint2 sg = make_uint2(0u, 0u), sh = make_uint2(0u, 0u);
+  if (tv) {
+    const uint8_t *pg = a.w4 + 1ll * row * (K >> 1) + (k_t >> 1);
+    const uint8_t *ph = pg + 8ll * (K >> 1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) wg[i] = ldg_stream(pg + 16 * i);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) wh[i] = ldg_stream(ph + 16 * i);
+    const uint8_t *qg = a.s4 + 1ll * row * (K >> 4) + (k_t >> 4);
+    sg = ldg_stream8(qg);
+    sh = ldg_stream8(qg + 8ll * (K >> 4));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) wg[i] = wh[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  // eight block scales per row -> broadcast half2
+  uint32_t sgb[8], shb[8];
+  {
+    const uint32_t gp[4] = {cvt_e4m3x2(sg.x), cvt_e4m3x2(sg.x >> 16), cvt_e4m3x2(sg.y), cvt_e4m3x2(sg.y >> 16)};
+    const uint32_t hp[4] = {cvt_e4m3x2(sh.x), cvt_e4m3x2(sh.x >> 16), cvt_e4m3x2(sh.y), cvt_e4m3x2(sh.y >> 16)};
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      sgb[b] = __byte_perm(gp[b >> 1], 0u, (b & 1) ? 0x3232u : 0x1010u);
+      shb[b] = __byte_perm(hp[b >> 1], 0u, (b & 1) ? 0x3232u : 0x1010u);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 xq[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        xq[n][j] = (tv && xr.valid[n]) ? ld_x16(xr.row[n] + k_t + 32 * i + 8 * j) : make_uint4(0u, 0u, 0u, 0u);
+    const uint32_t g4[4] = {wg[i].x, wg[i].y, wg[i].z, wg[i].w};
+    const uint32_t h4[4] = {wh[i].x, wh[i].y, wh[i].z, wh[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int blk = (4 * i + j) >> 1;
+      uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+      cvt_e2m1x8(g4[j], a0, a1, a2, a3);
+      cvt_e2m1x8(h4[j], b0, b1, b2, b3);
+      a0 = hmul2_u32(a0, sgb[blk]); a1 = hmul2_u32(a1, sgb[blk]);
+      a2 = hmul2_u32(a2, sgb[blk]); a3 = hmul2_u32(a3, sgb[blk]);
+      b0 = hmul2_u32(b0, shb[blk]); b1 = hmul2_u32(b1, shb[blk]);
+      b2 = hmul2_u32(b2, shb[blk]); b3 = hmul2_u32(b3, shb[blk]);
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        mma_16816(acc[n][0], a0, b0, a1, b1, xq[n][j].x, xq[n][j].y);
+        mma_16816(acc[n][1], a2, b2, a3, b3, xq[n][j].z, xq[n][j].w);
+      }
+    }
+  }
+}
+
+// ---- one batch of FP8: 16 rows x 256 k; this lane owns k_t .. k_t+63
+template <int NT>
+__device__ __forceinline__ void batch_fp8(float (&acc)[NT][2][4], const GemvArgs &a, const XRows<NT> &xr,
+                                          int row, int k_t, bool tv) {
+  const int K = a.K;
+  uint4 wg[4], wh[4];
+  if (tv) {
+    const uint8_t *pg = a.w8 + 1ll * row * K + k_t;
+    const uint8_t *ph = pg + 8ll * K;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) wg[i] = ldg_stream(pg + 16 * i);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) wh[i] = ldg_stream(ph + 16 * i);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) wg[i] = wh[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 xq[NT][2];
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        xq[n][j] = (tv && xr.valid[n]) ? ld_x16(xr.row[n] + k_t + 16 * i + 8 * j) : make_uint4(0u, 0u, 0u, 0u);
+    const uint32_t g4[4] = {wg[i].x, wg[i].y, wg[i].z, wg[i].w};
+    const uint32_t h4[4] = {wh[i].x, wh[i].y, wh[i].z, wh[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t a_lo, a_hi, b_lo, b_hi;
+      cvt_e4m3x4(g4[j], a_lo, a_hi);
+      cvt_e4m3x4(h4[j], b_lo, b_hi);
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        const uint4 xv = xq[n][j >> 1];
+        if (j & 1) mma_16816(acc[n][1], a_lo, b_lo, a_hi, b_hi, xv.z, xv.w);
+        else mma_16816(acc[n][0], a_lo, b_lo, a_hi, b_hi, xv.x, xv.y);
+      }
+    }
+  }
+}
+
+// ---- one batch of FP16: 16 rows x 128 k; this lane owns k_t .. k_t+31
+template <int NT>
+__device__ __forceinline__ void batch_fp16(float (&acc)[NT][2][4], const GemvArgs &a, const XRows<NT> &xr,
+                                           int row, int k_t, bool tv) {
+  const int K = a.K;
+  uint4 wg[4], wh[4];
+  if (tv) {
+    const __half *pg = a.w16 + 1ll * row * K + k_t;
+    const __half *ph = pg + 8ll * K;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) wg[i] = ldg_stream(pg + 8 * i);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) wh[i] = ldg_stream(ph + 8 * i);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) wg[i] = wh[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      const uint4 xv = (tv && xr.valid[n]) ? ld_x16(xr.row[n] + k_t + 8 * i) : make_uint4(0u, 0u, 0u, 0u);
+      mma_16816(acc[n][0], wg[i].x, wh[i].x, wg[i].y, wh[i].y, xv.x, xv.y);
+      mma_16816(acc[n][1], wg[i].z, wh[i].z, wg[i].w, wh[i].w, xv.z, xv.w);
+    }
+  }
 }
 
 // NT = number of 8-row activation groups (1: M <= 8, 2: M <= 16)
 template <int NT>
-__global__ void __launch_bounds__(kThreads, 2) gemv_stream_kernel(GemvArgs a, int tiles4, int tiles8,
-                                                                  int tiles16) {
-  extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ __align__(8) uint64_t bar_full[kStages];
-  __shared__ __align__(8) uint64_t bar_empty[kStages];
+__global__ void __maxnreg__(112) gemv_stream_kernel(GemvArgs a, int tiles4, int tiles8,
+                                                                  int tiles16, int l2_prefetch_on, int status_idx) {
+  constexpr int kMp = 8 * NT;                                // activation rows per slot entry
+  constexpr int kSlotFloats = kMmaWarps * kTileRows * kMp;   // [warp][row][m]
+  constexpr int kRing = 8 / NT;                              // flush ring depth (32 KB of slots)
+  __shared__ __align__(16) float ring[kRing * kSlotFloats];
+  __shared__ int meta_col[kMetaSegs * kTileRows];
+  __shared__ float meta_scl[kMetaSegs * kTileRows];
+  __shared__ float meta_bia[kMetaSegs * kTileRows];
+  __shared__ __align__(8) uint64_t bar_full[kRing];
+  __shared__ __align__(8) uint64_t bar_empty[kRing];
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -154,6 +334,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_stream_kernel(GemvArgs a, in
 
   Sched sc;
   sc.S = K / kSliceK;
+  sc.t4 = tiles4;
+  sc.t8 = tiles8;
   sc.e4 = tiles4 * sc.S;
   sc.e8 = sc.e4 + tiles8 * sc.S;
   sc.e16 = sc.e8 + tiles16 * sc.S;
@@ -163,12 +345,15 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_stream_kernel(GemvArgs a, in
   sc.G = gridDim.x;
   const int s_begin = sc.boundary(blockIdx.x);
   const int s_end = sc.boundary(blockIdx.x + 1);
-  int32_t *status = a.counters ? a.counters + (tiles4 + tiles8 + tiles16) : nullptr;
+  const int first_tile = s_begin / sc.S;
+  const int nseg = (s_end > s_begin) ? ((s_end - 1) / sc.S - first_tile + 1) : 0;
+  int32_t *status = a.counters + status_idx;
 
+  if (tid == 0) TL_MARK(0);
   if (tid == 0) {
-    for (int i = 0; i < kStages; ++i) {
-      mbar_init(smem_u32(&bar_full[i]), 1);
-      mbar_init(smem_u32(&bar_empty[i]), kMmaWarps);
+    for (int i = 0; i < kRing; ++i) {
+      mbar_init(smem_u32(&bar_full[i]), kMmaWarps);
+      mbar_init(smem_u32(&bar_empty[i]), 1);
     }
     mbar_init_fence();
   }
@@ -177,55 +362,139 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_stream_kernel(GemvArgs a, in
   // only prefetches its own weights until this grid has completed.
   pdl_launch_dependents();
 
-  const uint32_t smem_base = smem_u32(smem);
-
   if (warp == kMmaWarps) {
-    // ------------------------------------------------------------------ producer
-    int it = 0;
-    for (int s = s_begin; s < s_end; ++it) {
-      const Stage st = stage_at(sc, s, s_end);
-      const int slot = it % kStages;
-      if (it >= kStages) {
-        if (!mbar_wait(smem_u32(&bar_empty[slot]), ((it / kStages) - 1) & 1)) {
-          if (status && lane == 0) atomicExch(status, 1);
+    // ================================================================ epilogue warp
+    if (l2_prefetch_on) {
+      for (int i = 0; i < nseg; ++i) {
+        const Seg sg = seg_at(sc, s_begin, s_end, first_tile + i);
+        const uint8_t *base;
+        long long rb;      // row pitch in bytes
+        int b0, b1;        // byte range inside a row
+        if (sg.fmt == 0) { base = a.w4; rb = K >> 1; b0 = sg.k0 >> 1; b1 = sg.k1 >> 1; }
+        else if (sg.fmt == 1) { base = a.w8; rb = K; b0 = sg.k0; b1 = sg.k1; }
+        else { base = reinterpret_cast<const uint8_t *>(a.w16); rb = 2ll * K; b0 = sg.k0 * 2; b1 = sg.k1 * 2; }
+        if (sg.complete) {
+          if (lane == 0) l2_prefetch(base + sg.row0 * rb, static_cast<uint32_t>(kTileRows * rb));
+        } else if (lane < kTileRows) {
+          l2_prefetch(base + (sg.row0 + lane) * rb + b0, static_cast<uint32_t>(b1 - b0));
+        }
+        if (sg.fmt == 0 && lane == 16)
+          l2_prefetch(a.s4 + 1ll * sg.row0 * (K >> 4), static_cast<uint32_t>(kTileRows * (K >> 4)));
+      }
+    }
+    // output column, scale and bias of every row this CTA finishes: constants of the
+    // layer, fetched up front so that finishing a tile needs no global round trip
+    if (lane < kTileRows) {
+      for (int i = 0; i < nseg && i < kMetaSegs; ++i) {
+        const Seg sg = seg_at(sc, s_begin, s_end, first_tile + i);
+        const int prow = sg.gtile * kTileRows + lane;
+        const int col = a.perm ? a.perm[prow] : prow;
+        meta_col[i * kTileRows + lane] = col;
+        meta_scl[i * kTileRows + lane] = (sg.fmt == 1) ? a.s8[prow - a.n4] : (sg.fmt == 0 ? a.global4 : 1.f);
+        meta_bia[i * kTileRows + lane] = a.bias ? __half2float(a.bias[col]) : 0.f;
+      }
+    }
+    __syncwarp();
+    TL_MARK(1);
+    pdl_wait();  // y, workspace and flags belong to this launch only after the wait
+    TL_MARK(2);
+    const int row = lane & 15;
+    const int mh = lane >> 4;
+    const int mper = (M + 1) >> 1;
+    const int m_lo = mh * mper;
+    const int m_hi = min(M, m_lo + mper);
+    for (int q = 0; q < nseg; ++q) {
+      const int idx = seg_order(q, nseg);
+      const Seg sg = seg_at(sc, s_begin, s_end, first_tile + idx);
+      const int slot = q % kRing;
+      if (!mbar_wait(smem_u32(&bar_full[slot]), (q / kRing) & 1)) {
+        if (lane == 0) atomicExch(status, 2);
+        return;
+      }
+      const float *buf = ring + slot * kSlotFloats;
+      float sum[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int m = m_lo + i;
+        float v = 0.f;
+        if (m < m_hi) {
+#pragma unroll
+          for (int w = 0; w < kMmaWarps; ++w) v += buf[(w * kTileRows + row) * kMp + m];
+        }
+        sum[i] = v;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_empty[slot]));
+
+      if (!sg.starts) {
+        // continuation of a tile another CTA started: publish the partial, raise the flag
+        float *ws = a.workspace + 1ll * blockIdx.x * 256;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int m = m_lo + i;
+          if (m < m_hi) ws[row * 16 + m] = sum[i];
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) st_release_gpu(a.counters + blockIdx.x, 1);
+        TL_MARK(20 + (q < 10 ? q : 10));
+        continue;
+      }
+      if (!sg.ends) {
+        // this CTA holds the first slice of a split tile: collect the other parts in CTA order
+        const int b_last = sc.cta_of_slice(sg.gtile * sc.S + sc.S - 1);
+        bool ok = true;
+        for (int b = blockIdx.x + 1; b <= b_last && ok; ++b) {
+          int seen = 0;
+          if (lane == 0) {
+            for (int spin = 0; spin < 4000000; ++spin) {
+              if (ld_acquire_gpu(a.counters + b) != 0) { seen = 1; break; }
+            }
+          }
+          seen = __shfl_sync(0xffffffffu, seen, 0);
+          if (!seen) { ok = false; break; }
+          const float *pw = a.workspace + 1ll * b * 256;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int m = m_lo + i;
+            if (m < m_hi) sum[i] += ld_cg_f32(pw + row * 16 + m);
+          }
+          __syncwarp();
+          if (lane == 0) st_release_gpu(a.counters + b, 0);
+        }
+        if (!ok) {
+          if (lane == 0) atomicExch(status, 3);
           return;
         }
       }
-      const uint32_t full = smem_u32(&bar_full[slot]);
-      const uint32_t dst = smem_base + slot * kStageBytes;
-      const int row0 = st.tile * kTileRows;
-      const int k0 = st.sl * kSliceK;
-      const int kel = st.n * kSliceK;
-      uint32_t wbytes, sbytes = 0;
-      if (st.fmt == 0) { wbytes = kel >> 1; sbytes = kel >> 4; }
-      else if (st.fmt == 1) wbytes = kel;
-      else wbytes = kel << 1;
-      if (lane == 0) mbar_arrive_expect_tx(full, kTileRows * (wbytes + sbytes));
-      __syncwarp();
-      if (lane < kTileRows) {
-        const int r = row0 + lane;
-        const uint8_t *src;
-        if (st.fmt == 0) src = a.w4 + 1ll * r * (K >> 1) + (k0 >> 1);
-        else if (st.fmt == 1) src = a.w8 + 1ll * r * K + k0;
-        else src = reinterpret_cast<const uint8_t *>(a.w16) + (1ll * r * K + k0) * 2;
-        bulk_g2s(dst + lane * kRowPitch, src, wbytes, full);
-      } else if (st.fmt == 0) {
-        const int r = row0 + lane - kTileRows;
-        const uint8_t *src = a.s4 + 1ll * r * (K >> 4) + (k0 >> 4);
-        bulk_g2s(dst + kStageW + (lane - kTileRows) * kScalePitch, src, sbytes, full);
+      {
+        int col;
+        float scl, bia;
+        if (idx < kMetaSegs) {
+          col = meta_col[idx * kTileRows + row];
+          scl = meta_scl[idx * kTileRows + row];
+          bia = meta_bia[idx * kTileRows + row];
+        } else {
+          const int prow = sg.gtile * kTileRows + row;
+          col = a.perm ? a.perm[prow] : prow;
+          scl = (sg.fmt == 1) ? a.s8[prow - a.n4] : (sg.fmt == 0 ? a.global4 : 1.f);
+          bia = a.bias ? __half2float(a.bias[col]) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int m = m_lo + i;
+          if (m < m_hi) a.y[1ll * m * N + col] = __float2half_rn(fmaf(sum[i], scl, bia));
+        }
       }
-      s += st.n;
+      TL_MARK(20 + (q < 10 ? q : 10));
     }
+    TL_MARK(31);
     return;
   }
 
-  // -------------------------------------------------------------------- MMA warps
-  float *red = reinterpret_cast<float *>(smem + kStages * kStageBytes);
+  // ==================================================================== MMA warps
   const int g = lane >> 2;  // fragment row / activation row
   const int t = lane & 3;   // fragment k group
-  // ldmatrix source row and 16-byte column for this lane (x4: four 8x8 matrices)
-  const int lm_row = (lane & 7) + ((lane >> 3) & 1) * 8;
-  const int lm_sel = lane >> 4;
 
   float acc[NT][2][4];
 #pragma unroll
@@ -235,217 +504,81 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_stream_kernel(GemvArgs a, in
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[n][c][i] = 0.f;
 
-  // x is produced by the preceding kernel: do not touch it (or y) before this.
+  // x is produced by the preceding kernel: do not touch it before this.
   pdl_wait();
+  if (warp == 0) TL_MARK(3);
 
-  const __half *xrow[NT];
-  bool xvalid[NT];
+  XRows<NT> xr;
 #pragma unroll
   for (int n = 0; n < NT; ++n) {
     const int m = n * 8 + g;
-    xvalid[n] = m < M;
-    xrow[n] = a.x + 1ll * (xvalid[n] ? m : 0) * K;
+    xr.valid[n] = m < M;
+    xr.row[n] = a.x + 1ll * (xr.valid[n] ? m : 0) * K;
   }
 
-  int it = 0;
-  int seg = 0;        // index of the current tile segment of this CTA
-  int flush_buf = 0;
-  int s = s_begin;
-  bool failed = false;
-  while (s < s_end) {
-    const Stage st = stage_at(sc, s, s_end);
-    const int slot = it % kStages;
-    if (!mbar_wait(smem_u32(&bar_full[slot]), (it / kStages) & 1)) {
-      if (status && lane == 0) atomicExch(status, 2);
-      failed = true;
-      break;
-    }
-    const uint32_t sbase = smem_base + slot * kStageBytes;
-    const int k0 = st.sl * kSliceK;
-
-    if (st.fmt == 0) {
-      // pieces of 32 k (16 B per row); st.n pieces per warp
-      const int p0 = warp * st.n;
-      const uint8_t *sscale = smem + slot * kStageBytes + kStageW;
-      for (int j = 0; j < st.n; j += 2) {
-        const int p = p0 + j;
-        const bool two = (j + 1) < st.n;
-        uint32_t r0, r1, r2, r3;
-        ldmatrix_x4(sbase + lm_row * kRowPitch + (p + (two ? lm_sel : 0)) * 16, r0, r1, r2, r3);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          if (h == 1 && !two) break;
-          const int pp = p + h;
-          const uint32_t wg = h ? r2 : r0, wg8 = h ? r3 : r1;
-          // block scales: bytes (2pp, 2pp+1) of the scale row; this lane's 8 codes sit in block t>>1
-          const uint32_t sraw_g = *reinterpret_cast<const uint16_t *>(sscale + g * kScalePitch + 2 * pp);
-          const uint32_t sraw_g8 =
-              *reinterpret_cast<const uint16_t *>(sscale + (g + 8) * kScalePitch + 2 * pp);
-          const uint32_t sel = (t & 2) ? 0x3232u : 0x1010u;
-          const uint32_t sg = __byte_perm(cvt_e4m3x2(sraw_g), 0u, sel);
-          const uint32_t sg8 = __byte_perm(cvt_e4m3x2(sraw_g8), 0u, sel);
-          uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
-          cvt_e2m1x8(wg, a0, a1, a2, a3);
-          cvt_e2m1x8(wg8, b0, b1, b2, b3);
-          a0 = hmul2_u32(a0, sg); a1 = hmul2_u32(a1, sg); a2 = hmul2_u32(a2, sg); a3 = hmul2_u32(a3, sg);
-          b0 = hmul2_u32(b0, sg8); b1 = hmul2_u32(b1, sg8); b2 = hmul2_u32(b2, sg8); b3 = hmul2_u32(b3, sg8);
-          const int kk = k0 + pp * 32 + t * 8;
-#pragma unroll
-          for (int n = 0; n < NT; ++n) {
-            uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-            if (xvalid[n]) xv = ld_x16(xrow[n] + kk);
-            mma_16816(acc[n][0], a0, b0, a1, b1, xv.x, xv.y);
-            mma_16816(acc[n][1], a2, b2, a3, b3, xv.z, xv.w);
-          }
-        }
+  int base = 0;  // batches handed out before the current segment
+  for (int q = 0; q < nseg; ++q) {
+    const int idx = seg_order(q, nseg);
+    const Seg sg = seg_at(sc, s_begin, s_end, first_tile + idx);
+    const int first = (warp - base) & (kMmaWarps - 1);
+    const int row = sg.row0 + g;
+    if (sg.fmt == 0) {
+      for (int j = first; j < sg.nb; j += kMmaWarps) {
+        const int k_t = sg.k0 + j * 512 + t * 128;
+        batch_fp4<NT>(acc, a, xr, row, k_t, k_t < sg.k1);
       }
-    } else if (st.fmt == 1) {
-      // pieces of 16 k (16 B per row); 2*st.n pieces per warp
-      const int p0 = warp * 2 * st.n;
-      for (int j = 0; j < 2 * st.n; j += 2) {
-        const int p = p0 + j;
-        uint32_t r0, r1, r2, r3;
-        ldmatrix_x4(sbase + lm_row * kRowPitch + (p + lm_sel) * 16, r0, r1, r2, r3);
-        uint32_t a0, a4, a2, a6, c0, c4, c2, c6;
-        cvt_e4m3x4(r0, a0, a4);
-        cvt_e4m3x4(r1, a2, a6);
-        cvt_e4m3x4(r2, c0, c4);
-        cvt_e4m3x4(r3, c2, c6);
-        const int kk = k0 + p * 16 + t * 4;
-#pragma unroll
-        for (int n = 0; n < NT; ++n) {
-          uint2 x0 = make_uint2(0u, 0u), x1 = make_uint2(0u, 0u);
-          if (xvalid[n]) {
-            x0 = ld_x8(xrow[n] + kk);
-            x1 = ld_x8(xrow[n] + kk + 16);
-          }
-          mma_16816(acc[n][0], a0, a2, a4, a6, x0.x, x0.y);
-          mma_16816(acc[n][1], c0, c2, c4, c6, x1.x, x1.y);
-        }
+    } else if (sg.fmt == 1) {
+      for (int j = first; j < sg.nb; j += kMmaWarps) {
+        const int k_t = sg.k0 + j * 256 + t * 64;
+        batch_fp8<NT>(acc, a, xr, row, k_t, k_t < sg.k1);
       }
     } else {
-      // FP16: pieces of 16 k (32 B per row); 16 pieces per slice, 2 per warp
-      const int p0 = warp * 2 * st.n;
-      for (int j = 0; j < 2 * st.n; ++j) {
-        const int p = p0 + j;
-        uint32_t r0, r1, r2, r3;
-        ldmatrix_x4(sbase + lm_row * kRowPitch + p * 32 + lm_sel * 16, r0, r1, r2, r3);
-        const int kk = k0 + p * 16 + t * 2;
+      for (int j = first; j < sg.nb; j += kMmaWarps) {
+        const int k_t = sg.k0 + j * 128 + t * 32;
+        batch_fp16<NT>(acc, a, xr, row, k_t, k_t < sg.k1);
+      }
+    }
+    base += sg.nb;
+    if (warp == 0) TL_MARK(4 + (q < 14 ? q : 14));
+
+    // ---- hand the partial sums of this segment to the epilogue warp
+    const int slot = q % kRing;
+    if (q >= kRing) {
+      if (!mbar_wait(smem_u32(&bar_empty[slot]), ((q / kRing) - 1) & 1)) {
+        if (lane == 0) atomicExch(status, 1);
+        return;
+      }
+    }
+    float *buf = ring + slot * kSlotFloats;
 #pragma unroll
-        for (int n = 0; n < NT; ++n) {
-          uint32_t x0 = 0u, x1 = 0u;
-          if (xvalid[n]) {
-            x0 = ld_x4(xrow[n] + kk);
-            x1 = ld_x4(xrow[n] + kk + 8);
-          }
-          mma_16816(acc[n][j & 1], r0, r1, r2, r3, x0, x1);
-        }
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = g + (i >> 1) * 8;
+        const int m = n * 8 + 2 * t + (i & 1);
+        if (m < M) buf[(warp * kTileRows + r) * kMp + m] = acc[n][0][i] + acc[n][1][i];
+        acc[n][0][i] = 0.f;
+        acc[n][1][i] = 0.f;
       }
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(smem_u32(&bar_empty[slot]));
-    ++it;
-    s += st.n;
-
-    // ---- tile flush when the tile (or this CTA's range) ends
-    const bool tile_done = (st.sl + st.n == sc.S);
-    if (tile_done || s >= s_end) {
-      float *buf = red + flush_buf * kRedFloats;
-#pragma unroll
-      for (int n = 0; n < NT; ++n) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int row = g + (i >> 1) * 8;
-          const int m = n * 8 + 2 * t + (i & 1);
-          if (m < M) buf[(warp * kTileRows + row) * 16 + m] = acc[n][0][i] + acc[n][1][i];
-          acc[n][0][i] = 0.f;
-          acc[n][1][i] = 0.f;
-        }
-      }
-      consumer_bar();
-      if (warp == (seg & (kMmaWarps - 1))) {
-        // this warp finishes the tile: lane -> (row, half of the m range)
-        const int row = lane & 15;
-        const int mh = lane >> 4;
-        const int mper = (M + 1) >> 1;
-        const int m_lo = mh * mper;
-        const int m_hi = min(M, m_lo + mper);
-        float sum[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) sum[i] = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int m = m_lo + i;
-          if (m < m_hi) {
-            float v = 0.f;
-#pragma unroll
-            for (int w = 0; w < kMmaWarps; ++w) v += buf[(w * kTileRows + row) * 16 + m];
-            sum[i] = v;
-          }
-        }
-        // segment coverage of the tile
-        const int tile_first_slice = st.gtile * sc.S;
-        const int seg_first = max(s_begin, tile_first_slice);
-        const bool complete = (seg_first == tile_first_slice) && tile_done;
-        bool finalize = complete;
-        if (!complete) {
-          // split tile: publish the partial, last arriver sums all parts in CTA order
-          const int myslot = (seg == 0) ? 0 : 1;
-          float *ws = a.workspace + (1ll * (blockIdx.x * 2 + myslot)) * 256;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int m = m_lo + i;
-            if (m < m_hi) ws[row * 16 + m] = sum[i];
-          }
-          __threadfence();
-          __syncwarp();
-          int old = 0;
-          const int b_first = sc.cta_of_slice(tile_first_slice);
-          const int b_last = sc.cta_of_slice(tile_first_slice + sc.S - 1);
-          if (lane == 0) old = atomicAdd(a.counters + st.gtile, 1);
-          old = __shfl_sync(0xffffffffu, old, 0);
-          if (old == b_last - b_first) {
-            __threadfence();
-#pragma unroll
-            for (int i = 0; i < 8; ++i) sum[i] = 0.f;
-            for (int b = b_first; b <= b_last; ++b) {
-              const int bslot = (sc.boundary(b) >= tile_first_slice) ? 0 : 1;
-              const float *pw = a.workspace + (1ll * (b * 2 + bslot)) * 256;
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const int m = m_lo + i;
-                if (m < m_hi) sum[i] += ld_cg_f32(pw + row * 16 + m);
-              }
-            }
-            if (lane == 0) atomicExch(a.counters + st.gtile, 0);
-            finalize = true;
-          }
-        }
-        if (finalize) {
-          const int prow = st.gtile * kTileRows + row;  // permuted row index over all groups
-          const int col = a.perm ? a.perm[prow] : prow;
-          const float scl = (st.fmt == 1) ? a.s8[prow - a.n4] : (st.fmt == 0 ? a.global4 : 1.f);
-          const float bia = a.bias ? __half2float(a.bias[col]) : 0.f;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int m = m_lo + i;
-            if (m < m_hi) a.y[1ll * m * N + col] = __float2half_rn(fmaf(sum[i], scl, bia));
-          }
-        }
-      }
-      flush_buf ^= 1;
-      ++seg;
-    }
+    if (lane == 0) mbar_arrive(smem_u32(&bar_full[slot]));
   }
-  (void)failed;
 }
 
 }  // namespace
 
+#ifdef RDQ_TIMELINE
+extern "C" int rdq_debug_timeline(long long *host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_timeline, sizeof(long long) * 148 * 32) == cudaSuccess ? 0 : -3;
+}
+#endif
+
 void gemv_stream_scratch(int N, size_t *workspace_bytes, size_t *counter_bytes) {
   const int G = sm_count();
-  *workspace_bytes = static_cast<size_t>(G) * 2 * 256 * sizeof(float);
-  *counter_bytes = (static_cast<size_t>(N / kTileRows) + 2) * sizeof(int32_t);
+  (void)N;
+  *workspace_bytes = static_cast<size_t>(G) * 256 * sizeof(float);  // one partial tile per CTA
+  *counter_bytes = (static_cast<size_t>(G) + 2) * sizeof(int32_t);  // one flag per CTA + status word
 }
 
 bool gemv_stream_supported(const GemvArgs &a) {
@@ -457,41 +590,31 @@ bool gemv_stream_supported(const GemvArgs &a) {
   return true;
 }
 
-int launch_gemv_stream(const GemvArgs &a, bool pdl, cudaStream_t stream) {
-  static bool attr_set[64] = {};
-  int dev = 0;
-  RDQ_CUDA(cudaGetDevice(&dev));
-  if (dev < 64 && !attr_set[dev]) {
-    RDQ_CUDA(cudaFuncSetAttribute(gemv_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  kSmemBytes));
-    RDQ_CUDA(cudaFuncSetAttribute(gemv_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  kSmemBytes));
-    attr_set[dev] = true;
-  }
+int launch_gemv_stream(const GemvArgs &a, bool pdl, bool l2_prefetch_on, cudaStream_t stream) {
   const int tiles4 = a.n4 / kTileRows, tiles8 = a.n8 / kTileRows, tiles16 = a.n16 / kTileRows;
-  const long long slices = 1ll * (tiles4 + tiles8 + tiles16) * (a.K / kSliceK);
   // Every CTA must own at least one slice: a CTA's share of the weighted slice
   // line has to be no shorter than the heaviest slice (32 units).
-  const long long weight = 1ll * (a.K / kSliceK) * (1ll * tiles4 * kUnit4 + 1ll * tiles8 * kUnit8 + 1ll * tiles16 * kUnit16);
+  const long long weight =
+      1ll * (a.K / kSliceK) * (1ll * tiles4 * kUnit4 + 1ll * tiles8 * kUnit8 + 1ll * tiles16 * kUnit16);
   int G = sm_count();
   if (weight / kUnit16 < G) G = static_cast<int>(weight / kUnit16);
   if (G < 1) G = 1;
-  (void)slices;
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(G));
   cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  const int pf = l2_prefetch_on ? 1 : 0;
   if (a.M <= 8) {
-    RDQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<1>, a, tiles4, tiles8, tiles16));
+    RDQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<1>, a, tiles4, tiles8, tiles16, pf, sm_count()));
   } else {
-    RDQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<2>, a, tiles4, tiles8, tiles16));
+    RDQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<2>, a, tiles4, tiles8, tiles16, pf, sm_count()));
   }
   return RDQ_OK;
 }

@@ -48,7 +48,7 @@ int launch_gemv_generic(const GemvArgs &a, cudaStream_t stream);
 
 // True when the TMA-staged stream kernel accepts the shape / pointers.
 bool gemv_stream_supported(const GemvArgs &a);
-int launch_gemv_stream(const GemvArgs &a, bool pdl, cudaStream_t stream);
+int launch_gemv_stream(const GemvArgs &a, bool pdl, bool l2_prefetch_on, cudaStream_t stream);
 // workspace floats / counter ints the stream kernel needs for N output rows
 void gemv_stream_scratch(int N, size_t *workspace_bytes, size_t *counter_bytes);
 
