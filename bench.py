@@ -185,7 +185,7 @@ def main() -> None:
     ap.add_argument("--copies", type=int, default=6, help="rotating weight copies (L2 defeat)")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--kernel", default="stream", choices=["stream", "generic"])
+    ap.add_argument("--kernel", default="tiled", choices=["tiled", "stream", "generic"])
     ap.add_argument("--no-l2-prefetch", action="store_true")
     args = ap.parse_args()
 
@@ -214,7 +214,7 @@ def main() -> None:
     copies = max(args.copies, 2)
     layers = build_block(device, seed=rank, copies=copies)
     step_bytes = sum(l["bytes"] for l in layers)
-    flags = (_lib.RDQ_GEMV_STREAM if args.kernel == "stream" else _lib.RDQ_GEMV_GENERIC)
+    flags = {"tiled": _lib.RDQ_GEMV_AUTO, "stream": _lib.RDQ_GEMV_STREAM, "generic": _lib.RDQ_GEMV_GENERIC}[args.kernel]
     if not args.no_pdl:
         flags |= _lib.RDQ_GEMV_PDL
     if args.no_l2_prefetch:
@@ -326,7 +326,7 @@ def main() -> None:
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peak_kind,
-                     "frac_of_nominal_8tbs": achieved / 8000.0, "kernel": "gemv_stream_kernel",
+                     "frac_of_nominal_8tbs": achieved / 8000.0, "kernel": "gemv_%s_kernel" % args.kernel,
                      "bytes_per_launch": per_launch_bytes},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": sum(2 * m * l["k"] for l in layers),
                 "d2h_bytes_per_step": sum(2 * m * l["n"] for l in layers), "steps": e2e_steps,

@@ -115,6 +115,44 @@ int rdq_gemv_mixed(const void *x, int M,
                    int flags, void *stream);
 
 /*
+ * Tiled weight layout of the fast decode GEMV.  rdq_gemv_repack re-tiles the
+ * row-major checkpoint tensors once per layer into `w_tiled`
+ * (rdq_gemv_tiled_bytes bytes; 0 = shape has no tiled layout: groups must be
+ * multiples of 16 rows and K must split into equal chunks that are multiples
+ * of 64).  16 rows x one k chunk are stored as one contiguous block that is
+ * copied to shared memory by a single bulk-async (TMA) copy.  Plays the role
+ * of the reference's load-time Marlin repack
+ * (rdquant/fused_gemv_pack.py:151-172, :310-354).
+ */
+size_t rdq_gemv_tiled_bytes(int n_fp4, int n_fp8, int n_fp16, int K);
+int rdq_gemv_repack(const void *w_fp4, const void *w_fp4_scales,
+                    const void *w_fp8, const void *w_fp16,
+                    void *w_tiled,
+                    int n_fp4, int n_fp8, int n_fp16, int K, void *stream);
+
+/*
+ * Decode GEMV, M <= 16, on the tiled layout; same contract as rdq_gemv_mixed
+ * (y[m, perm[p]] = sum_k x[m,k] * W_perm[p,k] (+ bias), FP32 accumulation,
+ * deterministic).  Replaces the split-K kernels on repacked weights
+ * (rdquant/csrc/rdquant_ops.h:104-234).  workspace / counters are required
+ * (rdq_gemv_scratch_size).  Every 32-bit word of `workspace` must read
+ * 0xffffffff on first use (the mark for "no partial sum stored"); every
+ * completed launch leaves it in that state.  counters must be zero on first
+ * use; counters[SM count] is a status word that stays 0 unless a bounded
+ * device-side wait ran out.  Launches sharing one workspace / counters pair
+ * must be ordered on one stream.
+ * flags: RDQ_GEMV_PDL.
+ */
+int rdq_gemv_tiled(const void *x, int M,
+                   const void *w_tiled, const float *w_fp8_scales,
+                   float w_fp4_global_scale,
+                   const int32_t *perm, const void *bias,
+                   void *y,
+                   int n_fp4, int n_fp8, int n_fp16, int K,
+                   void *workspace, int32_t *counters,
+                   int flags, void *stream);
+
+/*
  * Prefill GEMM, any M >= 1 (meant for M >= 16):
  *   y[m, j] = sum_k x[m,k] * W[j,k] (+ bias[j]),  j in original channel order.
  * Weight tiles are gathered by inv_perm, dequantised to FP16 into shared

@@ -19,9 +19,11 @@ SOURCES = [
     "rdq_dequant.cu",
     "rdq_gemv_generic.cu",
     "rdq_gemv_stream.cu",
+    "rdq_gemv_tiled.cu",
     "rdq_gemm.cu",
 ]
-HEADERS = ["rdq_common.cuh", "rdq_kernels.cuh", os.path.join("..", "..", "include", "rdq_b200.h")]
+HEADERS = ["rdq_common.cuh", "rdq_kernels.cuh", "rdq_gemv_tiled_kernel.inl", "rdq_gemv_tiled_kernel2.inl",
+           os.path.join("..", "..", "include", "rdq_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
@@ -78,6 +80,12 @@ def _bind(lib: ctypes.CDLL) -> None:
     lib.rdq_gemv_scratch_size.argtypes = [i32, ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]
     lib.rdq_gemv_mixed.restype = i32
     lib.rdq_gemv_mixed.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp]
+    lib.rdq_gemv_tiled_bytes.restype = ctypes.c_size_t
+    lib.rdq_gemv_tiled_bytes.argtypes = [i32, i32, i32, i32]
+    lib.rdq_gemv_repack.restype = i32
+    lib.rdq_gemv_repack.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
+    lib.rdq_gemv_tiled.restype = i32
+    lib.rdq_gemv_tiled.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp]
     lib.rdq_gemm_mixed.restype = i32
     lib.rdq_gemm_mixed.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
 
@@ -88,6 +96,9 @@ EXPORTS = [
     "rdq_dequant_packed",
     "rdq_gemv_scratch_size",
     "rdq_gemv_mixed",
+    "rdq_gemv_tiled_bytes",
+    "rdq_gemv_repack",
+    "rdq_gemv_tiled",
     "rdq_gemm_mixed",
 ]
 

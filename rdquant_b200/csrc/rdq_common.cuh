@@ -123,23 +123,25 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+// One suspended wait on the barrier phase: the thread sleeps in hardware (it takes no
+// issue slots from the working warps) until the phase completes or about `ns`
+// nanoseconds have passed.
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity, uint32_t ns) {
   uint32_t ok;
   asm volatile(
       "{\n.reg .pred p;\n"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
       "selp.u32 %0, 1, 0, p;\n}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(ns)
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls (about a second) and reports
-// false, so a lost copy or a logic error cannot hang the device.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          uint32_t limit = 20000000u) {
+// Bounded wait: gives up after `limit` suspended waits of up to 0.1 ms each (about a
+// second) and reports false, so a lost copy or a logic error cannot hang the device.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = 10000u) {
   for (uint32_t i = 0; i < limit; ++i) {
-    if (mbar_test(bar, parity)) return true;
+    if (mbar_try(bar, parity, 100000u)) return true;
   }
   return false;
 }
@@ -171,7 +173,7 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t &r0, uint32_
 // D(16x8,f32) += A(16x16,f16,row) * B(16x8,f16,col)
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                           uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])

@@ -447,8 +447,9 @@ __global__ void __maxnreg__(112) gemv_stream_kernel(GemvArgs a, int tiles4, int 
         for (int b = blockIdx.x + 1; b <= b_last && ok; ++b) {
           int seen = 0;
           if (lane == 0) {
-            for (int spin = 0; spin < 4000000; ++spin) {
+            for (int spin = 0; spin < 2000000; ++spin) {
               if (ld_acquire_gpu(a.counters + b) != 0) { seen = 1; break; }
+              __nanosleep(200);
             }
           }
           seen = __shfl_sync(0xffffffffu, seen, 0);

@@ -1,0 +1,147 @@
+// Kernel part of rdq_gemv_tiled.cu (included at its end; see the header comment there).
+namespace rdq {
+
+namespace {
+
+// Image schedule, identical on every CTA.  Images are numbered in storage order.
+struct TSched {
+  int ck;            // chunk length in NVFP4 elements
+  int S4, S8, S16;   // images per tile in each group
+  int t4, t8;        // tiles in the NVFP4 / FP8 groups
+  int e4, e8, e16;   // end of each group's image range
+  int u4, u8;        // image weight (bytes / 16) of NVFP4 / other images
+  long long w4, w8, W;
+  int G;
+
+  __device__ __forceinline__ int image_of_pos(long long p) const {
+    if (p < w4) return static_cast<int>(p / u4);
+    if (p < W) return e4 + static_cast<int>((p - w4) / u8);
+    return e16;
+  }
+  __device__ __forceinline__ long long pos_of_image(int s) const {
+    if (s < e4) return 1ll * s * u4;
+    return w4 + 1ll * (s - e4) * u8;
+  }
+  __device__ __forceinline__ int boundary(int b) const {
+    if (b >= G) return e16;
+    return image_of_pos(W * b / G);
+  }
+  __device__ int cta_of_image(int s) const {
+    int b = static_cast<int>(pos_of_image(s) * G / W);
+    if (b >= G) b = G - 1;
+    while (b + 1 < G && boundary(b + 1) <= s) ++b;
+    while (b > 0 && boundary(b) > s) --b;
+    return b;
+  }
+  __device__ __forceinline__ int tile_of_image(int s) const {
+    if (s < e4) return s / S4;
+    if (s < e8) return t4 + (s - e4) / S8;
+    return t4 + t8 + (s - e8) / S16;
+  }
+  // byte offset of image s inside the tiled buffer
+  __device__ __forceinline__ long long image_offset(int s) const {
+    return pos_of_image(s) << 4;
+  }
+};
+
+// The images of one 16-row tile that this CTA streams.
+struct TSeg {
+  int fmt;        // 0 NVFP4, 1 FP8, 2 FP16
+  int gtile;      // tile index over all groups
+  int first_img;  // first image of the tile (global numbering)
+  int S;          // images in the tile
+  int c0, c1;     // chunk range of this CTA
+  bool starts, ends;
+};
+
+__device__ __forceinline__ TSeg tseg_at(const TSched &sc, int s_begin, int s_end, int gtile) {
+  TSeg sg;
+  sg.gtile = gtile;
+  if (gtile < sc.t4) {
+    sg.fmt = 0; sg.S = sc.S4; sg.first_img = gtile * sc.S4;
+  } else if (gtile < sc.t4 + sc.t8) {
+    sg.fmt = 1; sg.S = sc.S8; sg.first_img = sc.e4 + (gtile - sc.t4) * sc.S8;
+  } else {
+    sg.fmt = 2; sg.S = sc.S16; sg.first_img = sc.e8 + (gtile - sc.t4 - sc.t8) * sc.S16;
+  }
+  const int a = max(s_begin, sg.first_img), b = min(s_end, sg.first_img + sg.S);
+  sg.c0 = a - sg.first_img;
+  sg.c1 = b - sg.first_img;
+  sg.starts = (sg.c0 == 0);
+  sg.ends = (sg.c1 == sg.S);
+  return sg;
+}
+
+// processing order of a CTA's tile segments: the (possibly split) first tile, whose
+// partial another CTA is waiting for, then the (possibly split) last tile, which this
+// CTA finishes, then the whole tiles in between
+__device__ __forceinline__ int tseg_order(int q, int nseg) {
+  if (q == 0) return 0;
+  if (q == 1) return nseg - 1;
+  return q - 1;
+}
+
+__device__ __forceinline__ void t_st_release(int32_t *p, int32_t v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int32_t t_ld_acquire(const int32_t *p) {
+  int32_t v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float t_ld_cg(const float *p) {
+  float v;
+  asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+// x is written by the preceding kernel: coherent loads, issued only after the PDL wait
+__device__ __forceinline__ uint4 t_ldx16(const __half *p) {
+  uint4 v;
+  asm volatile("ld.global.L1::evict_last.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint2 t_ldx8(const __half *p) {
+  uint2 v;
+  asm volatile("ld.global.L1::evict_last.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t t_ldx4(const __half *p) {
+  uint32_t v;
+  asm volatile("ld.global.L1::evict_last.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+struct TiledArgs {
+  const __half *x;
+  int M;
+  const uint8_t *tiled;
+  const float *s8;
+  float global4;
+  const int32_t *perm;
+  const __half *bias;
+  __half *y;
+  int n4, n8, n16, K;
+  float *workspace;
+  int32_t *flags;  // one per CTA, then the status word at index status_idx
+  int status_idx;
+  int nstages;
+  int slot_bytes;
+};
+
+#ifdef RDQ_TIMELINE
+__device__ long long g_ttimeline[148 * 32];
+__device__ __forceinline__ void ttl_mark(int slot) {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  if (blockIdx.x < 148 && slot < 32) g_ttimeline[blockIdx.x * 32 + slot] = t;
+}
+#define TTL_MARK(slot) do { if ((threadIdx.x & 31) == 0) ttl_mark(slot); } while (0)
+#else
+#define TTL_MARK(slot) do { } while (0)
+#endif
+
+}  // namespace
+}  // namespace rdq
+
+#include "rdq_gemv_tiled_kernel2.inl"

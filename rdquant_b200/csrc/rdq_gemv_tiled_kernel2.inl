@@ -1,0 +1,564 @@
+// The tiled GEMV kernel proper (included from rdq_gemv_tiled_kernel.inl).
+namespace rdq {
+
+namespace {
+
+// Activation fragment loads: from the shared-memory copy (XS) or from global memory.
+// `base` is a shared-memory byte address (XS) or a generic pointer value.
+template <bool XS>
+__device__ __forceinline__ uint4 ldx16(uint64_t base, int byte_off) {
+  uint4 v;
+  if (XS) {
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(static_cast<uint32_t>(base) + byte_off) : "memory");
+  } else {
+    v = t_ldx16(reinterpret_cast<const __half *>(base + byte_off));
+  }
+  return v;
+}
+template <bool XS>
+__device__ __forceinline__ uint2 ldx8(uint64_t base, int byte_off) {
+  uint2 v;
+  if (XS) {
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];"
+                 : "=r"(v.x), "=r"(v.y) : "r"(static_cast<uint32_t>(base) + byte_off) : "memory");
+  } else {
+    v = t_ldx8(reinterpret_cast<const __half *>(base + byte_off));
+  }
+  return v;
+}
+template <bool XS>
+__device__ __forceinline__ uint32_t ldx4(uint64_t base, int byte_off) {
+  uint32_t v;
+  if (XS) {
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(static_cast<uint32_t>(base) + byte_off) : "memory");
+  } else {
+    v = t_ldx4(reinterpret_cast<const __half *>(base + byte_off));
+  }
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+
+// multiply-accumulate one NVFP4 piece (16 rows x 32 k): raw words of rows g / g+8, the
+// E4M3 scale pair of the piece for each row (low 16 bits), the lane's 8 activations
+template <int NT>
+__device__ __forceinline__ void fp4_piece(float (&acc)[NT][2][4], uint32_t wg, uint32_t wg8, uint32_t sraw_g,
+                                          uint32_t sraw_g8, uint32_t sel, const uint4 (&xv)[NT]) {
+  const uint32_t sg = __byte_perm(cvt_e4m3x2(sraw_g), 0u, sel);
+  const uint32_t sg8 = __byte_perm(cvt_e4m3x2(sraw_g8), 0u, sel);
+  uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+  cvt_e2m1x8(wg, a0, a1, a2, a3);
+  cvt_e2m1x8(wg8, b0, b1, b2, b3);
+  a0 = hmul2_u32(a0, sg); a1 = hmul2_u32(a1, sg); a2 = hmul2_u32(a2, sg); a3 = hmul2_u32(a3, sg);
+  b0 = hmul2_u32(b0, sg8); b1 = hmul2_u32(b1, sg8); b2 = hmul2_u32(b2, sg8); b3 = hmul2_u32(b3, sg8);
+#pragma unroll
+  for (int n = 0; n < NT; ++n) {
+    mma_16816(acc[n][0], a0, b0, a1, b1, xv[n].x, xv[n].y);
+    mma_16816(acc[n][1], a2, b2, a3, b3, xv[n].z, xv[n].w);
+  }
+}
+
+// Per-lane shared-memory addresses inside a stage, for the pair of pieces the warp starts with.
+// A "pair" is two 16-byte pieces of every row = one ldmatrix.x4.
+//
+// ---- NVFP4 stage: pairs [lo, hi) of 16 rows x 64 k.  All loads of a pair are issued
+// before its first use; addresses advance by constants.
+template <int NT, bool XS>
+__device__ __forceinline__ void stage_fp4(float (&acc)[NT][2][4], uint32_t lm_addr, uint32_t sc_addr,
+                                          uint32_t sc8_addr, const uint64_t (&xb)[NT], int xoff, int npairs,
+                                          uint32_t sel) {
+  for (int i = 0; i < npairs; ++i) {
+    uint32_t w[4];
+    ldmatrix_x4(lm_addr, w[0], w[1], w[2], w[3]);
+    const uint32_t s_g = lds_u32(sc_addr);    // scale bytes of pieces (p, p+1) for row g
+    const uint32_t s_g8 = lds_u32(sc8_addr);  // ... for row g + 8
+    uint4 x0[NT], x1[NT];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      x0[n] = ldx16<XS>(xb[n], xoff);
+      x1[n] = ldx16<XS>(xb[n], xoff + 64);
+    }
+    fp4_piece<NT>(acc, w[0], w[1], s_g, s_g8, sel, x0);
+    fp4_piece<NT>(acc, w[2], w[3], s_g >> 16, s_g8 >> 16, sel, x1);
+    lm_addr += 32;
+    sc_addr += 4;
+    sc8_addr += 4;
+    xoff += 128;
+  }
+}
+
+// ---- FP8 stage: pairs of 16 rows x 32 k
+template <int NT, bool XS>
+__device__ __forceinline__ void stage_fp8(float (&acc)[NT][2][4], uint32_t lm_addr, const uint64_t (&xb)[NT],
+                                          int xoff, int npairs) {
+  for (int i = 0; i < npairs; ++i) {
+    uint32_t w[4];
+    ldmatrix_x4(lm_addr, w[0], w[1], w[2], w[3]);
+    uint2 x0[NT], x1[NT];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      x0[n] = ldx8<XS>(xb[n], xoff);
+      x1[n] = ldx8<XS>(xb[n], xoff + 32);
+    }
+    uint32_t a0, a4, a2, a6, c0, c4, c2, c6;
+    cvt_e4m3x4(w[0], a0, a4);
+    cvt_e4m3x4(w[1], a2, a6);
+    cvt_e4m3x4(w[2], c0, c4);
+    cvt_e4m3x4(w[3], c2, c6);
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      mma_16816(acc[n][0], a0, a2, a4, a6, x0[n].x, x0[n].y);
+      mma_16816(acc[n][1], c0, c2, c4, c6, x1[n].x, x1[n].y);
+    }
+    lm_addr += 32;
+    xoff += 64;
+  }
+}
+
+// ---- FP16 stage: pairs of 16 rows x 16 k (32 B per row = two 16-byte pieces = one MMA)
+template <int NT, bool XS>
+__device__ __forceinline__ void stage_fp16(float (&acc)[NT][2][4], uint32_t lm_addr, const uint64_t (&xb)[NT],
+                                           int xoff, int npairs) {
+  for (int i = 0; i < npairs; ++i) {
+    uint32_t w[4];
+    ldmatrix_x4(lm_addr, w[0], w[1], w[2], w[3]);
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      const uint32_t x0 = ldx4<XS>(xb[n], xoff);
+      const uint32_t x1 = ldx4<XS>(xb[n], xoff + 16);
+      mma_16816(acc[n][i & 1], w[0], w[1], w[2], w[3], x0, x1);
+    }
+    lm_addr += 32;
+    xoff += 32;
+  }
+}
+
+// NT = number of 8-row activation groups (1: M <= 8, 2: M <= 16)
+template <int NT, bool XS>
+__global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledArgs a,
+                                                  const __grid_constant__ TSched sc) {
+  constexpr int kMp = 8 * NT;
+  constexpr int kFR = kFlushRing / NT;  // flush ring depth
+  constexpr int kSlotFloats = kMmaWarps * kTileRows * kMp;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(8) uint64_t bar_full[kMaxStages];
+  __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
+  __shared__ __align__(8) uint64_t fl_full[kFlushRing];
+  __shared__ __align__(8) uint64_t fl_empty[kFlushRing];
+  __shared__ __align__(8) uint64_t bar_x;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int K = a.K, M = a.M;
+  const int N = a.n4 + a.n8 + a.n16;
+  const int nst = a.nstages;
+  float *flush = reinterpret_cast<float *>(smem + nst * a.slot_bytes);
+  int *meta_col = reinterpret_cast<int *>(flush + kFR * kSlotFloats);
+  float *meta_scl = reinterpret_cast<float *>(meta_col + kMetaSegs * kTileRows);
+  float *meta_bia = meta_scl + kMetaSegs * kTileRows;
+  uint8_t *xsm = reinterpret_cast<uint8_t *>(meta_bia + kMetaSegs * kTileRows);
+  const int xpitch = 2 * a.K + 16;  // activation row pitch in shared memory: skewed against bank conflicts
+
+  const int s_begin = sc.boundary(blockIdx.x);
+  const int s_end = sc.boundary(blockIdx.x + 1);
+  const int first_tile = (s_end > s_begin) ? sc.tile_of_image(s_begin) : 0;
+  const int nseg = (s_end > s_begin) ? (sc.tile_of_image(s_end - 1) - first_tile + 1) : 0;
+  int32_t *status = a.flags + a.status_idx;
+  const int ck = sc.ck;
+  const int pitch = (ck >> 1) + 16;
+
+  if (tid == 0) {
+    TTL_MARK(0);
+    for (int i = 0; i < nst; ++i) {
+      mbar_init(smem_u32(&bar_full[i]), 1);
+      mbar_init(smem_u32(&bar_empty[i]), kMmaWarps);
+    }
+    for (int i = 0; i < kFR; ++i) {
+      mbar_init(smem_u32(&fl_full[i]), kMmaWarps);
+      mbar_init(smem_u32(&fl_empty[i]), 1);
+    }
+    mbar_init(smem_u32(&bar_x), 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+  // Let the next kernel in the stream become resident as early as possible; until this
+  // grid completes it only fills its own shared-memory ring with weights.
+  pdl_launch_dependents();
+
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (warp == kMmaWarps) {
+    // ==================================================================== producer
+    if (lane != 0) return;
+    // The ring is filled with weights first (they do not depend on the preceding kernel);
+    // only then wait for that kernel and fetch the activations it produced.
+    bool x_sent = false;
+    auto send_x = [&]() {
+      if (x_sent) return;
+      x_sent = true;
+      pdl_wait();
+      if (XS) {
+        const uint32_t bx = smem_u32(&bar_x);
+        mbar_arrive_expect_tx(bx, static_cast<uint32_t>(M) * 2u * K);
+        for (int m = 0; m < M; ++m) bulk_g2s(smem_u32(xsm) + m * xpitch, a.x + 1ll * m * K, 2u * K, bx);
+      }
+    };
+    int it = 0, slot = 0, round = 0;
+    for (int q = 0; q < nseg; ++q) {
+      const TSeg sg = tseg_at(sc, s_begin, s_end, first_tile + tseg_order(q, nseg));
+      const uint32_t bytes = static_cast<uint32_t>(img_bytes(sg.fmt, ck));
+      for (int c = sg.c0; c < sg.c1; ++c, ++it) {
+        if (round > 0) {
+          send_x();
+          if (!mbar_wait(smem_u32(&bar_empty[slot]), (round - 1) & 1)) {
+            atomicExch(status, 1);
+            return;
+          }
+        }
+        const uint32_t full = smem_u32(&bar_full[slot]);
+        mbar_arrive_expect_tx(full, bytes);
+        bulk_g2s(smem_base + slot * a.slot_bytes, a.tiled + sc.image_offset(sg.first_img + c), bytes, full);
+        if (++slot == nst) { slot = 0; ++round; }
+      }
+    }
+    send_x();
+    return;
+  }
+
+  if (warp == kMmaWarps + 1) {
+    // ================================================================ epilogue warp
+    // output column, scale and bias of every row this CTA finishes: constants of the
+    // layer, fetched up front so that finishing a tile needs no global round trip
+    {
+      const int nmeta = min(nseg, kMetaSegs) * kTileRows;
+      for (int base = 0; base < nmeta; base += 128) {
+        int col[4];
+        float scl[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int item = base + u * 32 + lane;
+          col[u] = 0;
+          scl[u] = 1.f;
+          if (item < nmeta) {
+            const int gt = first_tile + (item >> 4);
+            const int prow = gt * kTileRows + (item & 15);
+            col[u] = a.perm ? a.perm[prow] : prow;
+            scl[u] = (gt < sc.t4) ? a.global4 : (gt < sc.t4 + sc.t8 ? a.s8[prow - a.n4] : 1.f);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int item = base + u * 32 + lane;
+          if (item < nmeta) {
+            meta_col[item] = col[u];
+            meta_scl[item] = scl[u];
+            meta_bia[item] = a.bias ? __half2float(a.bias[col[u]]) : 0.f;
+          }
+        }
+      }
+    }
+    __syncwarp();
+    TTL_MARK(1);
+    pdl_wait();  // y, workspace and flags belong to this launch only after the wait
+    TTL_MARK(2);
+    const int row = lane & 15;
+    const int mh = lane >> 4;
+    const int mper = (M + 1) >> 1;
+    const int m_lo = mh * mper;
+    const int m_hi = min(M, m_lo + mper);
+    for (int q = 0; q < nseg; ++q) {
+      const int idx = tseg_order(q, nseg);
+      const TSeg sg = tseg_at(sc, s_begin, s_end, first_tile + idx);
+      const int slot = q % kFR;
+      if (!mbar_wait(smem_u32(&fl_full[slot]), (q / kFR) & 1)) {
+        if (lane == 0) atomicExch(status, 2);
+        return;
+      }
+      const float *buf = flush + slot * kSlotFloats;
+      float sum[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int m = m_lo + i;
+        float v = 0.f;
+        if (m < m_hi) {
+#pragma unroll
+          for (int w = 0; w < kMmaWarps; ++w) v += buf[(w * kTileRows + row) * kMp + m];
+        }
+        sum[i] = v;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&fl_empty[slot]));
+
+      if (!sg.starts) {
+        // continuation of a tile another CTA started: store the partial sums into this
+        // CTA's workspace slot (idle words read 0xffffffff); the owner polls them
+        float *ws = a.workspace + 1ll * blockIdx.x * 256;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int m = m_lo + i;
+          if (m < m_hi) ws[row * 16 + m] = sum[i];
+        }
+        TTL_MARK(20 + (q < 10 ? q : 10));
+        continue;
+      }
+      if (!sg.ends) {
+        // this CTA holds the first image of a split tile: collect the other parts in CTA order
+        const int b_last = sc.cta_of_image(sg.first_img + sg.S - 1);
+        bool ok = true;
+        for (int b = blockIdx.x + 1; b <= b_last; ++b) {
+          float *pw = a.workspace + 1ll * b * 256;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int m = m_lo + i;
+            if (m < m_hi) {
+              uint32_t bits = 0xffffffffu;
+              for (int spin = 0; spin < 2000000 && bits == 0xffffffffu; ++spin) {
+                asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(bits) : "l"(pw + row * 16 + m) : "memory");
+                if (bits == 0xffffffffu) __nanosleep(200);
+              }
+              if (bits == 0xffffffffu) ok = false;
+              sum[i] += __uint_as_float(bits);
+              pw[row * 16 + m] = __uint_as_float(0xffffffffu);  // slot idle again
+            }
+          }
+        }
+        if (__any_sync(0xffffffffu, !ok)) {
+          if (lane == 0) atomicExch(status, 3);
+          return;
+        }
+      }
+      {
+        int col;
+        float scl, bia;
+        if (idx < kMetaSegs) {
+          col = meta_col[idx * kTileRows + row];
+          scl = meta_scl[idx * kTileRows + row];
+          bia = meta_bia[idx * kTileRows + row];
+        } else {
+          const int prow = sg.gtile * kTileRows + row;
+          col = a.perm ? a.perm[prow] : prow;
+          scl = (sg.fmt == 1) ? a.s8[prow - a.n4] : (sg.fmt == 0 ? a.global4 : 1.f);
+          bia = a.bias ? __half2float(a.bias[col]) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int m = m_lo + i;
+          if (m < m_hi) a.y[1ll * m * N + col] = __float2half_rn(fmaf(sum[i], scl, bia));
+        }
+      }
+      TTL_MARK(20 + (q < 10 ? q : 10));
+    }
+    TTL_MARK(31);
+    return;
+  }
+
+  // ==================================================================== MMA warps
+  const int g = lane >> 2;  // fragment row / activation row
+  const int t = lane & 3;   // fragment k group
+  // ldmatrix.x4: lanes 0-7 / 8-15 address rows 0-7 / 8-15 of the first piece of a pair,
+  // lanes 16-31 the same rows of the second piece
+  const uint32_t lm_lane = ((lane & 7) + ((lane >> 3) & 1) * 8) * pitch + (lane >> 4) * 16;
+  const int spitch = scale_pitch(ck);
+  const uint32_t sc_lane = kTileRows * pitch + g * spitch;  // block scales of row g
+  const uint32_t sel = (t & 2) ? 0x3232u : 0x1010u;          // this lane's 8 codes sit in block t >> 1
+  const int npair = ck >> 6;                                 // pairs of 16-byte pieces per row
+
+  float acc[NT][2][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n)
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[n][c][i] = 0.f;
+
+  // x is produced by the preceding kernel: do not touch it before this.
+  pdl_wait();
+  if (warp == 0) TTL_MARK(3);
+
+  // Lanes of activation rows >= M read row 0 instead: their output columns are never stored.
+  uint64_t xb[NT];
+  if (XS) {
+    // the producer thread copies the activation rows into shared memory (bulk copies)
+    if (!mbar_wait(smem_u32(&bar_x), 0)) {
+      if (lane == 0) atomicExch(status, 6);
+      return;
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      const int m = n * 8 + g;
+      xb[n] = smem_u32(xsm) + (m < M ? m : 0) * xpitch;
+    }
+  } else {
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      const int m = n * 8 + g;
+      xb[n] = reinterpret_cast<uint64_t>(a.x + 1ll * (m < M ? m : 0) * K);
+    }
+  }
+
+#ifdef RDQ_TIMELINE
+  long long cyc_wait = 0, cyc_comp = 0, cyc_flush = 0, tprev = clock64();
+  if (warp == 0) TTL_MARK(15);
+#define TTL_LAP(acc_) do { const long long tnow_ = clock64(); acc_ += tnow_ - tprev; tprev = tnow_; } while (0)
+#else
+#define TTL_LAP(acc_) do { } while (0)
+#endif
+  int it = 0, slot = 0, round = 0;
+  for (int q = 0; q < nseg; ++q) {
+    const TSeg sg = tseg_at(sc, s_begin, s_end, first_tile + tseg_order(q, nseg));
+    for (int c = sg.c0; c < sg.c1; ++c, ++it) {
+      TTL_LAP(cyc_flush);
+      if (!mbar_wait(smem_u32(&bar_full[slot]), round & 1)) {
+        if (lane == 0) atomicExch(status, 4);
+        return;
+      }
+      TTL_LAP(cyc_wait);
+      const uint32_t sbase = smem_base + slot * a.slot_bytes;
+      // the warps take turns on the pair ranges from stage to stage, so uneven splits average out
+      int lw = warp + it * 5;
+      lw -= (lw / kMmaWarps) * kMmaWarps;
+      if (sg.fmt == 0) {
+        const int lo = lw * npair / kMmaWarps, hi = (lw + 1) * npair / kMmaWarps;
+        stage_fp4<NT, XS>(acc, sbase + lm_lane + lo * 32, sbase + sc_lane + lo * 4, sbase + sc_lane + 8 * spitch + lo * 4,
+                          xb, 2 * (c * ck + lo * 64 + t * 8), hi - lo, sel);
+      } else if (sg.fmt == 1) {
+        const int lo = lw * npair / kMmaWarps, hi = (lw + 1) * npair / kMmaWarps;
+        stage_fp8<NT, XS>(acc, sbase + lm_lane + lo * 32, xb, 2 * (c * (ck >> 1) + lo * 32 + t * 4), hi - lo);
+      } else {
+        const int lo = lw * npair / kMmaWarps, hi = (lw + 1) * npair / kMmaWarps;
+        stage_fp16<NT, XS>(acc, sbase + lm_lane + lo * 32, xb, 2 * (c * (ck >> 2) + lo * 16 + t * 2), hi - lo);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_empty[slot]));
+      if (++slot == nst) { slot = 0; ++round; }
+      TTL_LAP(cyc_comp);
+    }
+    if (warp == 0) TTL_MARK(4 + (q < 10 ? q : 10));
+
+    // ---- hand the partial sums of this segment to the epilogue warp
+    const int fslot = q % kFR;
+    if (q >= kFR && !mbar_wait(smem_u32(&fl_empty[fslot]), ((q / kFR) - 1) & 1)) {
+      if (lane == 0) atomicExch(status, 5);
+      return;
+    }
+    float *buf = flush + fslot * kSlotFloats;
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = g + (i >> 1) * 8;
+        const int m = n * 8 + 2 * t + (i & 1);
+        if (m < M) buf[(warp * kTileRows + r) * kMp + m] = acc[n][0][i] + acc[n][1][i];
+        acc[n][0][i] = 0.f;
+        acc[n][1][i] = 0.f;
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&fl_full[fslot]));
+  }
+#ifdef RDQ_TIMELINE
+  if (warp == 0 && lane == 0 && blockIdx.x < 148) {
+    g_ttimeline[blockIdx.x * 32 + 16] = cyc_wait;
+    g_ttimeline[blockIdx.x * 32 + 17] = cyc_comp;
+    g_ttimeline[blockIdx.x * 32 + 18] = cyc_flush;
+    g_ttimeline[blockIdx.x * 32 + 19] = it;
+  }
+#endif
+}
+
+}  // namespace
+
+#ifdef RDQ_TIMELINE
+extern "C" int rdq_debug_timeline_tiled(long long *host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_ttimeline, sizeof(long long) * 148 * 32) == cudaSuccess ? 0 : -3;
+}
+#endif
+
+void gemv_tiled_scratch(size_t *workspace_bytes, size_t *flag_bytes) {
+  const int G = sm_count();
+  *workspace_bytes = static_cast<size_t>(G) * 256 * sizeof(float);  // one partial tile per CTA
+  *flag_bytes = (static_cast<size_t>(G) + 2) * sizeof(int32_t);     // status word at index G
+}
+
+int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
+  const int ck = tiled_chunk_k(h.K);
+  TSched sc;
+  sc.ck = ck;
+  sc.S4 = h.K / ck;
+  sc.S8 = sc.S4 * 2;
+  sc.S16 = sc.S4 * 4;
+  sc.t4 = h.n4 / kTileRows;
+  sc.t8 = h.n8 / kTileRows;
+  const int t16 = h.n16 / kTileRows;
+  sc.e4 = sc.t4 * sc.S4;
+  sc.e8 = sc.e4 + sc.t8 * sc.S8;
+  sc.e16 = sc.e8 + t16 * sc.S16;
+  sc.u4 = img_bytes(0, ck) / 16;
+  sc.u8 = img_bytes(1, ck) / 16;
+  sc.w4 = 1ll * sc.e4 * sc.u4;
+  sc.w8 = sc.w4 + 1ll * (sc.e8 - sc.e4) * sc.u8;
+  sc.W = sc.w8 + 1ll * (sc.e16 - sc.e8) * sc.u8;
+  // every CTA must own at least one image: its share may not be shorter than the
+  // heaviest image
+  int G = sm_count();
+  const long long maxg = sc.W / (sc.u4 > sc.u8 ? sc.u4 : sc.u8);
+  if (maxg < G) G = static_cast<int>(maxg);
+  if (G < 1) G = 1;
+  sc.G = G;
+
+  TiledArgs a;
+  a.x = h.x; a.M = h.M; a.tiled = h.tiled; a.s8 = h.s8; a.global4 = h.global4; a.perm = h.perm;
+  a.bias = h.bias; a.y = h.y; a.n4 = h.n4; a.n8 = h.n8; a.n16 = h.n16; a.K = h.K;
+  a.workspace = h.workspace; a.flags = h.flags;
+  a.status_idx = sm_count();
+  a.slot_bytes = (img_bytes(0, ck) + 127) & ~127;
+  const int nt = h.M <= 8 ? 1 : 2;
+  // shared memory: weight ring | flush ring | output metadata | activations (if they fit)
+  const int fixed = (kFlushRing / nt) * kMmaWarps * kTileRows * 8 * nt * 4 + kMetaSegs * kTileRows * 12;
+  const int total_budget = 110 * 1024;  // two CTAs (this layer's and the next one's) share an SM
+  int xbytes = h.M * (2 * h.K + 16);
+  bool xs = true;
+  if (fixed + xbytes + 2 * a.slot_bytes > total_budget || xbytes > 44 * 1024) {
+    xs = false;
+    xbytes = 0;
+  }
+  int nst = (total_budget - fixed - xbytes) / a.slot_bytes;
+  if (nst > kMaxStages) nst = kMaxStages;
+  if (nst < 2) nst = 2;
+  a.nstages = nst;
+  const int smem = nst * a.slot_bytes + fixed + xbytes;
+
+  static int smem_set[64][4] = {};
+  int dev = 0;
+  RDQ_CUDA(cudaGetDevice(&dev));
+  const int variant = (nt - 1) * 2 + (xs ? 1 : 0);
+  const void *fn = variant == 0 ? reinterpret_cast<const void *>(gemv_tiled_kernel<1, false>)
+                   : variant == 1 ? reinterpret_cast<const void *>(gemv_tiled_kernel<1, true>)
+                   : variant == 2 ? reinterpret_cast<const void *>(gemv_tiled_kernel<2, false>)
+                                  : reinterpret_cast<const void *>(gemv_tiled_kernel<2, true>);
+  if (dev < 64 && smem_set[dev][variant] < smem) {
+    RDQ_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    smem_set[dev][variant] = smem;
+  }
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(G));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  void *params[2] = {&a, &sc};
+  RDQ_CUDA(cudaLaunchKernelExC(&cfg, fn, params));
+  return RDQ_OK;
+}
+
+}  // namespace rdq

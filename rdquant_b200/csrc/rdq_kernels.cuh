@@ -52,6 +52,28 @@ int launch_gemv_stream(const GemvArgs &a, bool pdl, bool l2_prefetch_on, cudaStr
 // workspace floats / counter ints the stream kernel needs for N output rows
 void gemv_stream_scratch(int N, size_t *workspace_bytes, size_t *counter_bytes);
 
+// ---- tiled layout (rdq_gemv_tiled.cu)
+struct GemvTiledArgs {
+  const __half *x;
+  int M;
+  const uint8_t *tiled;
+  const float *s8;
+  float global4;
+  const int32_t *perm;
+  const __half *bias;
+  __half *y;
+  int n4, n8, n16, K;
+  float *workspace;
+  int32_t *flags;
+};
+int tiled_chunk_k(int K);
+bool tiled_supported(int n4, int n8, int n16, int K);
+size_t tiled_bytes(int n4, int n8, int n16, int K);
+int launch_repack(const void *w_fp4, const void *w_fp4_scales, const void *w_fp8, const void *w_fp16,
+                  void *tiled_out, int n4, int n8, int n16, int K, cudaStream_t stream);
+void gemv_tiled_scratch(size_t *workspace_bytes, size_t *flag_bytes);
+int launch_gemv_tiled(const GemvTiledArgs &a, bool pdl, cudaStream_t stream);
+
 int launch_gemm(const GemmArgs &a, cudaStream_t stream);
 
 }  // namespace rdq

@@ -70,7 +70,7 @@ def validate_layer_data(layer_data: dict, splits: dict, k: int) -> tuple[int, in
 
 
 def pack_for_fused_gemv(layer_data: dict, splits: dict, k: int, device,
-                        honor_global_scale: bool = False) -> Optional[dict]:
+                        honor_global_scale: bool = False, tiled: bool = True) -> Optional[dict]:
     """Device buffers for ``rdquant_cuda.mixed_gemv`` / ``mixed_gemm``.
 
     Accepts any split (single-format layers, an FP16 group, groups below 128 channels);
@@ -100,7 +100,7 @@ def pack_for_fused_gemv(layer_data: dict, splits: dict, k: int, device,
     if honor_global_scale and "nvfp4_global_scale" in layer_data:
         gs = float(layer_data["nvfp4_global_scale"].item())
     workspace, counters = rdquant_cuda.gemv_scratch(n, device)
-    return {
+    fd = {
         "w_fp4_q": dev(layer_data["weight_nvfp4"], torch.uint8) if n4 else None,
         "w_fp4_scales": dev(layer_data["weight_nvfp4_scale"], torch.uint8) if n4 else None,
         "w_fp4_global_scale": gs,
@@ -115,6 +115,9 @@ def pack_for_fused_gemv(layer_data: dict, splits: dict, k: int, device,
         "parallel_k": 1,
         "n_fp4": n4, "n_fp8": n8, "n_fp16": n16, "k": int(k),
     }
+    # re-tiled copy for the fast decode kernel (None when the shape has no tiled layout)
+    fd["w_tiled"] = rdquant_cuda.repack_tiled(fd) if tiled else None
+    return fd
 
 
 def packed_weight_bytes(splits: dict, k: int) -> int:

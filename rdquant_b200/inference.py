@@ -22,7 +22,7 @@ from rdquant_b200.fused_gemv_pack import (
     pack_for_fused_gemv,
 )
 
-_FD_TENSORS = ("w_fp4_q", "w_fp4_scales", "w_fp8_q", "w_fp8_scales", "w_fp16", "perm", "inv_perm",
+_FD_TENSORS = ("w_fp4_q", "w_fp4_scales", "w_fp8_q", "w_fp8_scales", "w_fp16", "w_tiled", "perm", "inv_perm",
                "workspace", "tile_counters")
 
 

@@ -71,7 +71,8 @@ def gemv_scratch(n_out: int, device) -> tuple[torch.Tensor, torch.Tensor]:
     with _on_device(device):
         _lib.check(_lib.lib().rdq_gemv_scratch_size(int(n_out), ctypes.byref(ws), ctypes.byref(cnt)),
                    "rdq_gemv_scratch_size")
-    workspace = torch.empty(max(ws.value // 4, 1), dtype=torch.float32, device=device)
+    # idle workspace words read 0xffffffff (the tiled kernel's "no partial sum yet" mark)
+    workspace = torch.full((max(ws.value // 4, 1),), -1, dtype=torch.int32, device=device).view(torch.float32)
     counters = torch.zeros(max(cnt.value // 4, 1), dtype=torch.int32, device=device)
     return workspace, counters
 
@@ -125,9 +126,28 @@ def dequantize_packed(layer_data: dict, splits: dict, k: int, inv_perm: Optional
     return out
 
 
+def repack_tiled(fd: dict) -> Optional[torch.Tensor]:
+    """Re-tile the row-major buffers of a ``pack_for_fused_gemv`` dict for the fast GEMV;
+    ``None`` when the shape has no tiled layout."""
+    n4, n8, n16, k = fd["n_fp4"], fd["n_fp8"], fd["n_fp16"], fd["k"]
+    nbytes = int(_lib.lib().rdq_gemv_tiled_bytes(n4, n8, n16, k))
+    if nbytes == 0:
+        return None
+    some = next(t for t in (fd.get("w_fp4_q"), fd.get("w_fp8_q"), fd.get("w_fp16")) if t is not None)
+    out = torch.empty(nbytes, dtype=torch.uint8, device=some.device)
+    with _on_device(some.device):
+        rc = _lib.lib().rdq_gemv_repack(_ptr(fd.get("w_fp4_q")), _ptr(fd.get("w_fp4_scales")), _ptr(fd.get("w_fp8_q")),
+                                        _ptr(fd.get("w_fp16")), _ptr(out), n4, n8, n16, k, _stream(some.device))
+    _lib.check(rc, "rdq_gemv_repack")
+    return out
+
+
 def mixed_gemv(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None, flags: int = 0,
                out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``y[M, N] = x[M, K] @ W.T (+ bias)`` for M <= 16 from a ``pack_for_fused_gemv`` dict."""
+    """``y[M, N] = x[M, K] @ W.T (+ bias)`` for M <= 16 from a ``pack_for_fused_gemv`` dict.
+
+    Runs on the tiled layout when the dict carries one (``w_tiled``) and ``flags`` does not
+    force one of the row-major kernels."""
     _need_cuda("x", x, torch.float16)
     if x.dim() != 2:
         raise RuntimeError("x must be 2-D [M, K]")
@@ -143,6 +163,14 @@ def mixed_gemv(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None, f
         if bias.numel() != n:
             raise RuntimeError("bias must have N elements")
     y = out if out is not None else torch.empty(m, n, dtype=torch.float16, device=x.device)
+    if fd.get("w_tiled") is not None and (flags & 15) == _lib.RDQ_GEMV_AUTO:
+        with _on_device(x.device):
+            rc = _lib.lib().rdq_gemv_tiled(
+                _ptr(x), m, _ptr(fd["w_tiled"]), _ptr(fd.get("w_fp8_scales")), float(fd.get("w_fp4_global_scale", 1.0)),
+                _ptr(fd.get("perm")), _ptr(bias), _ptr(y), n4, n8, n16, k, _ptr(fd.get("workspace")),
+                _ptr(fd.get("tile_counters")), int(flags), _stream(x.device))
+        _lib.check(rc, "rdq_gemv_tiled")
+        return y
     with _on_device(x.device):
         rc = _lib.lib().rdq_gemv_mixed(
             _ptr(x), m, _ptr(fd.get("w_fp4_q")), _ptr(fd.get("w_fp4_scales")), float(fd.get("w_fp4_global_scale", 1.0)),

@@ -1,0 +1,79 @@
+"""Column-parallel sharding + all-gather on two gloo ranks (CPU).  The per-rank product is
+computed by the oracle here (no GPU in this test): what is under test is the host logic --
+row ranges, local splits, the gather buffer layout and the index that restores original
+channel order."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import golden_layer_torch, golden_layers
+from oracle import oracle_np as onp
+from rdquant_b200.parallel import ColumnParallelPlan, gather_outputs, split_points
+
+
+def test_split_points():
+    assert split_points(0, 4) == [0, 0, 0, 0, 0]
+    assert split_points(640, 8) == [0, 0, 128, 128, 256, 384, 384, 512, 640]
+    pts = split_points(6528, 8)
+    assert pts[0] == 0 and pts[-1] == 6528 and all(p % 128 == 0 for p in pts)
+    sizes = [b - a for a, b in zip(pts, pts[1:])]
+    assert max(sizes) - min(sizes) <= 128
+    assert split_points(100, 2) == [0, 0, 100]  # one short tile goes to the last rank
+
+
+def test_plan_covers_every_channel_once():
+    gen = torch.Generator().manual_seed(0)
+    splits = {"NVFP4": 640, "FP8": 256, "FP16": 128}
+    inv = torch.randperm(1024, generator=gen)
+    for world in (1, 2, 4, 8):
+        plan = ColumnParallelPlan.build(splits, inv, world)
+        assert sum(plan.n_local) == 1024
+        assert plan.gather_index.unique().numel() == 1024
+        assert int(plan.gather_index.max()) < world * plan.n_max
+        for r in range(world):
+            assert sum(plan.local_splits(r).values()) == plan.n_local[r]
+
+
+def _worker(rank, world, port, case_name, out_q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        case = golden_layers()[case_name]
+        layer, splits, k = golden_layer_torch(case)
+        plan = ColumnParallelPlan.build(splits, layer["inv_permutation"], world, align=16)
+        shard = plan.shard_layer_data(layer, rank)
+        x = torch.from_numpy(case["x3_f16_bits"].copy()).view(torch.int16).view(torch.float16)
+        if plan.n_local[rank]:
+            y_local = onp.mixed_precision_linear(x.numpy(), onp.torch_layer_to_np(shard), plan.local_splits(rank), k)
+        else:
+            y_local = np.zeros((3, 0), dtype=np.float32)
+        y = gather_outputs(torch.from_numpy(y_local), plan)
+        y_full = onp.mixed_precision_linear(x.numpy(), onp.torch_layer_to_np(layer), splits, k)
+        out_q.put((rank, float(np.abs(y.numpy() - y_full).max()), list(plan.n_local)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("case_name", ["mixed_384x256", "alloc_96x64"])
+def test_two_rank_gather_matches_full_layer(case_name):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, case_name, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, err, n_local in results:
+        assert err < 1e-5, (rank, err)
+        assert sum(n_local) == sum(int(v) for v in golden_layers()[case_name]["splits"])
