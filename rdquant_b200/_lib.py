@@ -22,7 +22,7 @@ SOURCES = [
     "rdq_gemv_tiled.cu",
     "rdq_gemm.cu",
 ]
-HEADERS = ["rdq_common.cuh", "rdq_kernels.cuh", "rdq_gemv_tiled_kernel.inl", "rdq_gemv_tiled_kernel2.inl",
+HEADERS = ["rdq_common.cuh", "rdq_kernels.cuh", "rdq_gemv_tiled_kernel.inl", "rdq_gemv_tiled_kernel2.inl", "rdq_gemm_kernel.inl",
            os.path.join("..", "..", "include", "rdq_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

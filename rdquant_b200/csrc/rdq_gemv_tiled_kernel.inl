@@ -130,13 +130,15 @@ struct TiledArgs {
 };
 
 #ifdef RDQ_TIMELINE
-__device__ long long g_ttimeline[148 * 32];
-__device__ __forceinline__ void ttl_mark(int slot) {
+__device__ long long g_ttimeline[4 * 148 * 32];
+__device__ int g_tl_base_dummy;
+#define g_tl_base (((ttl_m - 1) & 3) * 148 * 32)
+__device__ __forceinline__ void ttl_mark_(int slot, int ttl_m) {
   long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  if (blockIdx.x < 148 && slot < 32) g_ttimeline[blockIdx.x * 32 + slot] = t;
+  if (blockIdx.x < 148 && slot < 32) g_ttimeline[g_tl_base + blockIdx.x * 32 + slot] = t;
 }
-#define TTL_MARK(slot) do { if ((threadIdx.x & 31) == 0) ttl_mark(slot); } while (0)
+#define TTL_MARK(slot) do { if ((threadIdx.x & 31) == 0) ttl_mark_(slot, a.M); } while (0)
 #else
 #define TTL_MARK(slot) do { } while (0)
 #endif

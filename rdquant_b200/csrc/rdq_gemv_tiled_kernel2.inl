@@ -463,10 +463,11 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
   }
 #ifdef RDQ_TIMELINE
   if (warp == 0 && lane == 0 && blockIdx.x < 148) {
-    g_ttimeline[blockIdx.x * 32 + 16] = cyc_wait;
-    g_ttimeline[blockIdx.x * 32 + 17] = cyc_comp;
-    g_ttimeline[blockIdx.x * 32 + 18] = cyc_flush;
-    g_ttimeline[blockIdx.x * 32 + 19] = it;
+    const int ttl_m = a.M;
+    g_ttimeline[g_tl_base + blockIdx.x * 32 + 16] = cyc_wait;
+    g_ttimeline[g_tl_base + blockIdx.x * 32 + 17] = cyc_comp;
+    g_ttimeline[g_tl_base + blockIdx.x * 32 + 18] = cyc_flush;
+    g_ttimeline[g_tl_base + blockIdx.x * 32 + 19] = it;
   }
 #endif
 }
@@ -475,7 +476,7 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
 
 #ifdef RDQ_TIMELINE
 extern "C" int rdq_debug_timeline_tiled(long long *host_out) {
-  return cudaMemcpyFromSymbol(host_out, g_ttimeline, sizeof(long long) * 148 * 32) == cudaSuccess ? 0 : -3;
+  return cudaMemcpyFromSymbol(host_out, g_ttimeline, sizeof(long long) * 4 * 148 * 32) == cudaSuccess ? 0 : -3;
 }
 #endif
 

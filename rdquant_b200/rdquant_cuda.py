@@ -15,7 +15,7 @@ import torch
 from rdquant_b200 import _lib
 
 MAX_GEMV_M = 16
-GEMM_READY = False
+GEMM_READY = True
 
 
 def _ptr(t: Optional[torch.Tensor]):

@@ -1,0 +1,74 @@
+"""Prefill GEMM (tcgen05) through the C ABI against the oracle: golden layers, random byte
+patterns, the benchmark block shapes, ragged M, bias."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import ORDER, golden_layer_torch
+from oracle import oracle_np as onp
+from rdquant_b200 import rdquant_cuda
+from rdquant_b200.fused_gemv_pack import pack_for_fused_gemv
+from rdquant_b200.synthetic import QWEN3_4B_BLOCK, fixed_splits, random_packed_layer
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3  # max |y - y_ref| / max |y_ref|, FP32-accumulation reference
+
+
+def _run(layer, splits, k, m, bias=False, seed=0):
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randn(m, k, generator=gen).half()
+    n = sum(splits.values())
+    b = (torch.randn(n, generator=gen) * 0.5).half() if bias else None
+    fd = pack_for_fused_gemv(layer, splits, k, "cuda", tiled=False)
+    y = rdquant_cuda.mixed_gemm(x.cuda(), fd, b.cuda() if bias else None)
+    torch.cuda.synchronize()
+    y_ref = onp.mixed_precision_linear(x.numpy(), onp.torch_layer_to_np(layer), splits, k,
+                                       b.float().numpy() if bias else None)
+    return y.cpu().float().numpy(), y_ref
+
+
+def test_golden_layers(layers):
+    for name, case in layers.items():
+        layer, splits, k = golden_layer_torch(case)
+        if k % 64:
+            with pytest.raises(RuntimeError):
+                _run(layer, splits, k, 32)
+            continue
+        for m in (1, 17, 130):
+            y, y_ref = _run(layer, splits, k, m, bias="bias" in layer, seed=m)
+            assert onp.rel_err(y, y_ref) < TOL, (name, m)
+
+
+@pytest.mark.parametrize("m", [16, 100, 128, 300])
+@pytest.mark.parametrize("shape", [(128, 128, 128, 256), (64, 32, 16, 512), (256, 0, 0, 1024), (0, 48, 0, 256),
+                                   (0, 0, 32, 768), (49, 46, 1, 64), (1664, 768, 128, 4096)])
+def test_random_bytes(shape, m):
+    n4, n8, n16, k = shape
+    layer = random_packed_layer(n4, n8, n16, k, seed=k + m)
+    splits = dict(zip(ORDER, (n4, n8, n16)))
+    y, y_ref = _run(layer, splits, k, m, bias=(m % 2 == 0), seed=m)
+    assert onp.rel_err(y, y_ref) < TOL
+
+
+@pytest.mark.parametrize("name", list(QWEN3_4B_BLOCK))
+def test_block_shapes_m512(name):
+    k, n = QWEN3_4B_BLOCK[name]
+    splits = fixed_splits(n)
+    layer = random_packed_layer(splits["NVFP4"], splits["FP8"], splits["FP16"], k, seed=len(name))
+    y, y_ref = _run(layer, splits, k, 512, bias=True, seed=3)
+    assert onp.rel_err(y, y_ref) < TOL, name
+
+
+def test_matches_dequantised_weight_matmul():
+    # size-independent property: GEMM == x @ dequant(W)^T with the bit-exact dequantisation kernel
+    k, n = 2560, 4096
+    splits = fixed_splits(n)
+    layer = random_packed_layer(splits["NVFP4"], splits["FP8"], splits["FP16"], k, seed=9)
+    fd = pack_for_fused_gemv(layer, splits, k, "cuda", tiled=False)
+    dev = {kk: v.cuda() for kk, v in layer.items()}
+    w = rdquant_cuda.dequantize_packed(dev, splits, k, inv_perm=dev["inv_permutation"])
+    x = torch.randn(2048, k, device="cuda").half()
+    y = rdquant_cuda.mixed_gemm(x, fd)
+    ref = x.float() @ w.float().T
+    err = (y.float() - ref).abs().max() / ref.abs().max()
+    assert float(err) < TOL
