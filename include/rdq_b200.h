@@ -153,6 +153,31 @@ int rdq_gemv_tiled(const void *x, int M,
                    int flags, void *stream);
 
 /*
+ * rdq_gemv_tiled for callers that cannot allocate device memory.  (No
+ * counterpart in the reference.)  Some hosts of this library run where
+ * cudaMalloc is off limits: inside a stream capture, inside another
+ * framework's allocator callback, or in a runtime whose memory budget is fixed
+ * at start-up.  This variant takes no scratch pointers: the partial-tile slots
+ * and the status word live in a device array that is part of the library image
+ * (about 165 KB, held by every GPU that loads the library until the process
+ * exits) and is sized for GPUs with up to 160 SMs; a larger GPU gets
+ * RDQ_E_UNSUPPORTED and a message.  The call itself performs no cudaMalloc,
+ * cudaFree or other allocating call.
+ * The first call on each device looks up the array's device address and clears
+ * it on `stream`; make that first call before any stream capture begins.  All
+ * calls on a device share the one array: calls that may overlap on the GPU
+ * (different streams, no ordering) race on it and must be serialised by the
+ * caller.  Results are identical to rdq_gemv_tiled.
+ */
+int rdq_gemv_tiled_noalloc(const void *x, int M,
+                           const void *w_tiled, const float *w_fp8_scales,
+                           float w_fp4_global_scale,
+                           const int32_t *perm, const void *bias,
+                           void *y,
+                           int n_fp4, int n_fp8, int n_fp16, int K,
+                           int flags, void *stream);
+
+/*
  * Prefill GEMM, any M >= 1 (meant for M >= 16):
  *   y[m, j] = sum_k x[m,k] * W[j,k] (+ bias[j]),  j in original channel order.
  * Weight tiles are gathered by inv_perm, dequantised to FP16 into shared

@@ -86,6 +86,8 @@ def _bind(lib: ctypes.CDLL) -> None:
     lib.rdq_gemv_repack.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
     lib.rdq_gemv_tiled.restype = i32
     lib.rdq_gemv_tiled.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp]
+    lib.rdq_gemv_tiled_noalloc.restype = i32
+    lib.rdq_gemv_tiled_noalloc.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, i32, i32, i32, i32, i32, vp]
     lib.rdq_gemm_mixed.restype = i32
     lib.rdq_gemm_mixed.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
 
@@ -99,6 +101,7 @@ EXPORTS = [
     "rdq_gemv_tiled_bytes",
     "rdq_gemv_repack",
     "rdq_gemv_tiled",
+    "rdq_gemv_tiled_noalloc",
     "rdq_gemm_mixed",
 ]
 

@@ -175,6 +175,36 @@ int rdq_gemv_tiled(const void *x, int M, const void *w_tiled, const float *w_fp8
   return launch_gemv_tiled(a, (flags & RDQ_GEMV_PDL) != 0, static_cast<cudaStream_t>(stream));
 }
 
+int rdq_gemv_tiled_noalloc(const void *x, int M, const void *w_tiled, const float *w_fp8_scales,
+                           float w_fp4_global_scale, const int32_t *perm, const void *bias, void *y, int n_fp4,
+                           int n_fp8, int n_fp16, int K, int flags, void *stream) {
+  RDQ_REQUIRE(n_fp4 >= 0 && n_fp8 >= 0 && n_fp16 >= 0 && K > 0, RDQ_E_INVALID, "bad layer shape");
+  RDQ_REQUIRE(M >= 0 && M <= RDQ_MAX_GEMV_M, RDQ_E_UNSUPPORTED,
+              "rdq_gemv_tiled_noalloc takes 1..%d activation rows, got M=%d", RDQ_MAX_GEMV_M, M);
+  if (M == 0 || n_fp4 + n_fp8 + n_fp16 == 0) return RDQ_OK;
+  RDQ_REQUIRE(tiled_supported(n_fp4, n_fp8, n_fp16, K), RDQ_E_UNSUPPORTED,
+              "shape has no tiled layout (K=%d, n=%d/%d/%d)", K, n_fp4, n_fp8, n_fp16);
+  RDQ_REQUIRE(x && y && w_tiled, RDQ_E_INVALID, "x, y and w_tiled must not be null");
+  RDQ_REQUIRE(aligned16(x) && aligned16(w_tiled), RDQ_E_INVALID, "x and w_tiled must be 16-byte aligned");
+  RDQ_REQUIRE(n_fp8 == 0 || w_fp8_scales != nullptr, RDQ_E_INVALID, "w_fp8_scales must not be null when n_fp8 > 0");
+  GemvTiledArgs a;
+  a.x = static_cast<const __half *>(x);
+  a.M = M;
+  a.tiled = static_cast<const uint8_t *>(w_tiled);
+  a.s8 = w_fp8_scales;
+  a.global4 = w_fp4_global_scale;
+  a.perm = perm;
+  a.bias = static_cast<const __half *>(bias);
+  a.y = static_cast<__half *>(y);
+  a.n4 = n_fp4;
+  a.n8 = n_fp8;
+  a.n16 = n_fp16;
+  a.K = K;
+  a.workspace = nullptr;
+  a.flags = nullptr;
+  return gemv_tiled_noalloc(a, (flags & RDQ_GEMV_PDL) != 0, static_cast<cudaStream_t>(stream));
+}
+
 int rdq_gemm_mixed(const void *x, int M, const void *w_fp4, const void *w_fp4_scales,
                    float w_fp4_global_scale, const void *w_fp8, const float *w_fp8_scales,
                    const void *w_fp16, const int32_t *inv_perm, const void *bias, void *y, int n_fp4,

@@ -562,4 +562,42 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
   return RDQ_OK;
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Entry point for callers that cannot allocate device memory (no counterpart in the
+// reference).  Its scratch -- the per-CTA partial-tile slots and the status word the
+// tiled GEMV needs -- lives in the array below, which every GPU that loads this library
+// holds until the process exits.  Sized for GPUs with up to kNoAllocMaxCtas SMs.
+// ---------------------------------------------------------------------------------------
+namespace {
+constexpr int kNoAllocMaxCtas = 160;
+constexpr int kNoAllocWsWords = kNoAllocMaxCtas * 256;  // workspace: one 16 x 16 float slot per CTA
+constexpr int kNoAllocCntWords = kNoAllocMaxCtas + 32;  // flags + status word
+static __device__ __align__(256) uint32_t g_noalloc_scratch[kNoAllocWsWords + kNoAllocCntWords];
+}  // namespace
+
+int gemv_tiled_noalloc(const GemvTiledArgs &in, bool pdl, cudaStream_t stream) {
+  static void *dev_ptr[64] = {};
+  int dev = 0;
+  RDQ_CUDA(cudaGetDevice(&dev));
+  RDQ_REQUIRE(dev >= 0 && dev < 64, RDQ_E_UNSUPPORTED, "device index %d is beyond the 64 devices this entry point tracks", dev);
+  RDQ_REQUIRE(sm_count() <= kNoAllocMaxCtas, RDQ_E_UNSUPPORTED,
+              "built-in scratch holds %d CTA slots but this GPU has %d SMs; use rdq_gemv_tiled with caller scratch",
+              kNoAllocMaxCtas, sm_count());
+  if (!dev_ptr[dev]) {
+    // Set-up, once per device, with that device current.  In host code the array's name is
+    // only a stand-in; the address a kernel can use has to come from the runtime.
+    void *p = nullptr;
+    RDQ_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    // idle partial-sum slots read 0xffffffff; flags and status word start at zero
+    RDQ_CUDA(cudaMemsetAsync(p, 0xff, sizeof(uint32_t) * kNoAllocWsWords, stream));
+    RDQ_CUDA(cudaMemsetAsync(static_cast<uint32_t *>(p) + kNoAllocWsWords, 0, sizeof(uint32_t) * kNoAllocCntWords, stream));
+    dev_ptr[dev] = p;
+  }
+  GemvTiledArgs a = in;
+  a.workspace = static_cast<float *>(dev_ptr[dev]);
+  a.flags = reinterpret_cast<int32_t *>(static_cast<uint32_t *>(dev_ptr[dev]) + kNoAllocWsWords);
+  return launch_gemv_tiled(a, pdl, stream);
+}
+
 }  // namespace rdq

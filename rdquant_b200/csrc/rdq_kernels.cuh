@@ -73,6 +73,8 @@ int launch_repack(const void *w_fp4, const void *w_fp4_scales, const void *w_fp8
                   void *tiled_out, int n4, int n8, int n16, int K, cudaStream_t stream);
 void gemv_tiled_scratch(size_t *workspace_bytes, size_t *flag_bytes);
 int launch_gemv_tiled(const GemvTiledArgs &a, bool pdl, cudaStream_t stream);
+// same kernel with the scratch in a library-owned device array (no allocation anywhere)
+int gemv_tiled_noalloc(const GemvTiledArgs &a, bool pdl, cudaStream_t stream);
 
 int launch_gemm(const GemmArgs &a, cudaStream_t stream);
 
