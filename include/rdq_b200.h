@@ -155,9 +155,9 @@ int rdq_gemv_tiled(const void *x, int M,
 /*
  * rdq_gemv_tiled for callers that cannot allocate device memory.  (No
  * counterpart in the reference.)  Some hosts of this library run where
- * cudaMalloc is off limits: inside a stream capture, inside another
- * framework's allocator callback, or in a runtime whose memory budget is fixed
- * at start-up.  This variant takes no scratch pointers: the partial-tile slots
+ * cudaMalloc is off limits: serving loops that forbid allocation once they
+ * are warm, code called from another framework's allocator callbacks, or a
+ * runtime whose device-memory budget is fixed at start-up.  This variant takes no scratch pointers: the partial-tile slots
  * and the status word live in a device array that is part of the library image
  * (about 165 KB, held by every GPU that loads the library until the process
  * exits) and is sized for GPUs with up to 160 SMs; a larger GPU gets
