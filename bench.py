@@ -95,29 +95,42 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_block(device, seed: int, copies: int):
-    """`copies` independent device copies of the seven packed layers of one block."""
+FUSE_GROUPS = [["q_proj", "k_proj", "v_proj"], ["o_proj"], ["gate_proj", "up_proj"], ["down_proj"]]
+
+
+def build_block(device, seed: int, copies: int, fuse: bool):
+    """`copies` independent device copies of the packed linears of one block.  With `fuse`,
+    projections that read the same input (q/k/v, gate/up) are packed as one layer each."""
     import torch
 
-    from rdquant_b200.fused_gemv_pack import layer_data_from_qweight, pack_for_fused_gemv, packed_weight_bytes
+    from rdquant_b200.fused_gemv_pack import fuse_layers, layer_data_from_qweight, pack_for_fused_gemv, packed_weight_bytes
     from rdquant_b200.quantize import quantize_weight
     from rdquant_b200.synthetic import QWEN3_4B_BLOCK, fixed_splits, synthetic_weight
 
-    layers = []
+    per_layer = {}
     for li, name in enumerate(LAYER_ORDER):
         k, n = QWEN3_4B_BLOCK[name]
         gen = torch.Generator().manual_seed(seed * 100 + li)
         w = synthetic_weight(n, k, gen)
         perm = torch.randperm(n, generator=gen)
         splits = fixed_splits(n)
-        # encode on the GPU (torch ops; offline step), pack once, clone per copy
+        # encode on the GPU (torch ops; offline step)
         qw = quantize_weight(w.to(device).float(), perm.to(device), splits)
-        data = layer_data_from_qweight(qw)
-        fds = [pack_for_fused_gemv({kk: v.clone() for kk, v in data.items()}, splits, k, device) for _ in range(copies)]
-        layers.append({"name": name, "k": k, "n": n, "splits": splits, "fds": fds,
-                       "bytes": packed_weight_bytes(splits, k), "qw": qw if li == 4 else None})
+        per_layer[name] = (layer_data_from_qweight(qw), splits, k, n)
         del w, qw
-    return layers
+    groups = FUSE_GROUPS if fuse else [[n] for n in LAYER_ORDER]
+    units = []
+    for group in groups:
+        k = per_layer[group[0]][2]
+        nbytes = sum(packed_weight_bytes(per_layer[g][1], k) for g in group)
+        if len(group) > 1:
+            data, splits = fuse_layers([(per_layer[g][0], per_layer[g][1]) for g in group])
+        else:
+            data, splits = per_layer[group[0]][0], per_layer[group[0]][1]
+        fds = [pack_for_fused_gemv({kk: v.clone() for kk, v in data.items()}, splits, k, device) for _ in range(copies)]
+        units.append({"name": "+".join(group), "k": k, "n": sum(per_layer[g][3] for g in group), "splits": splits,
+                      "fds": fds, "bytes": nbytes})
+    return units
 
 
 def cpu_baseline(budget_s: float = 12.0) -> dict:
@@ -187,6 +200,7 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel", default="tiled", choices=["tiled", "stream", "generic"])
     ap.add_argument("--no-l2-prefetch", action="store_true")
+    ap.add_argument("--no-fuse", action="store_true", help="seven launches per step instead of four")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -212,7 +226,7 @@ def main() -> None:
 
     steps, warmup, m = max(args.steps, 1), max(args.warmup, 3), args.m
     copies = max(args.copies, 2)
-    layers = build_block(device, seed=rank, copies=copies)
+    layers = build_block(device, seed=rank, copies=copies, fuse=not args.no_fuse)
     step_bytes = sum(l["bytes"] for l in layers)
     flags = {"tiled": _lib.RDQ_GEMV_AUTO, "stream": _lib.RDQ_GEMV_STREAM, "generic": _lib.RDQ_GEMV_GENERIC}[args.kernel]
     if not args.no_pdl:
@@ -316,6 +330,8 @@ def main() -> None:
         "config": {
             "workload": f"qwen3-4b decoder block: q,k,v,o,gate,up,down mixed-precision linears, M={m} decode GEMV "
                         "(BASELINE configs[1])",
+            "launches_per_step": len(layers),
+            "fusion": "none" if args.no_fuse else "q/k/v and gate/up packed as one layer each (they read the same input)",
             "split": "67/32/1 NVFP4/FP8/FP16, 128-aligned, random channel permutation",
             "bytes_per_step": step_bytes, "l2_policy": f"{copies} rotating weight copies = "
             f"{copies * step_bytes / 1e6:.0f} MB > 2 x L2; inputs larger than L2, no flush",

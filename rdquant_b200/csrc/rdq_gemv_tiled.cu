@@ -16,7 +16,8 @@
 //                   shared-memory ring, mbarrier tracked.  It starts BEFORE
 //                   griddepcontrol.wait: under programmatic dependent launch the
 //                   ring of this layer fills while the preceding kernel runs.
-//   12 MMA warps    split the k pieces of a stage; ldmatrix the packed bytes,
+//   12 MMA warps    in 3 groups of 4; stage i goes to group i % 3, whose warps split its k
+//                   pieces; ldmatrix the packed bytes,
 //                   convert with the hardware E2M1 / E4M3 -> f16 converters, scale
 //                   NVFP4 by its block scale (exact in f16) and issue mma.sync
 //                   m16n8k16 with the 16 weight rows as the row operand and the
@@ -44,6 +45,9 @@ namespace {
 
 constexpr int kTileRows = 16;
 constexpr int kMmaWarps = 12;
+constexpr int kGroups = 3;          // warp groups; stage i is consumed by group i % 3
+constexpr int kWarpsPerGroup = 4;   // power of two
+static_assert(kGroups * kWarpsPerGroup == kMmaWarps, "warp groups must cover the MMA warps");
 constexpr int kThreads = (kMmaWarps + 2) * 32;  // + producer warp + epilogue warp
 constexpr int kFlushRing = 4;
 constexpr int kMetaSegs = 32;

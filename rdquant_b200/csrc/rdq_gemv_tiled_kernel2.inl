@@ -176,7 +176,7 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
     TTL_MARK(0);
     for (int i = 0; i < nst; ++i) {
       mbar_init(smem_u32(&bar_full[i]), 1);
-      mbar_init(smem_u32(&bar_empty[i]), kMmaWarps);
+      mbar_init(smem_u32(&bar_empty[i]), kWarpsPerGroup);
     }
     for (int i = 0; i < kFR; ++i) {
       mbar_init(smem_u32(&fl_full[i]), kMmaWarps);
@@ -367,6 +367,7 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
   const uint32_t sc_lane = kTileRows * pitch + g * spitch;  // block scales of row g
   const uint32_t sel = (t & 2) ? 0x3232u : 0x1010u;          // this lane's 8 codes sit in block t >> 1
   const int npair = ck >> 6;                                 // pairs of 16-byte pieces per row
+  const int grp = warp / kWarpsPerGroup, wq = warp % kWarpsPerGroup;
 
   float acc[NT][2][4];
 #pragma unroll
@@ -412,6 +413,12 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
   for (int q = 0; q < nseg; ++q) {
     const TSeg sg = tseg_at(sc, s_begin, s_end, first_tile + tseg_order(q, nseg));
     for (int c = sg.c0; c < sg.c1; ++c, ++it) {
+      // stages go round robin to the warp groups: a warp then has a whole quarter of a stage
+      // to work on per barrier wait
+      if (it % kGroups != grp) {
+        if (++slot == nst) { slot = 0; ++round; }
+        continue;
+      }
       TTL_LAP(cyc_flush);
       if (!mbar_wait(smem_u32(&bar_full[slot]), round & 1)) {
         if (lane == 0) atomicExch(status, 4);
@@ -419,18 +426,17 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
       }
       TTL_LAP(cyc_wait);
       const uint32_t sbase = smem_base + slot * a.slot_bytes;
-      // the warps take turns on the pair ranges from stage to stage, so uneven splits average out
-      int lw = warp + it * 5;
-      lw -= (lw / kMmaWarps) * kMmaWarps;
+      // inside a group the warps take turns on the pair ranges, so uneven splits average out
+      const int lw = (wq + it / kGroups) & (kWarpsPerGroup - 1);
       if (sg.fmt == 0) {
-        const int lo = lw * npair / kMmaWarps, hi = (lw + 1) * npair / kMmaWarps;
+        const int lo = lw * npair / kWarpsPerGroup, hi = (lw + 1) * npair / kWarpsPerGroup;
         stage_fp4<NT, XS>(acc, sbase + lm_lane + lo * 32, sbase + sc_lane + lo * 4, sbase + sc_lane + 8 * spitch + lo * 4,
                           xb, 2 * (c * ck + lo * 64 + t * 8), hi - lo, sel);
       } else if (sg.fmt == 1) {
-        const int lo = lw * npair / kMmaWarps, hi = (lw + 1) * npair / kMmaWarps;
+        const int lo = lw * npair / kWarpsPerGroup, hi = (lw + 1) * npair / kWarpsPerGroup;
         stage_fp8<NT, XS>(acc, sbase + lm_lane + lo * 32, xb, 2 * (c * (ck >> 1) + lo * 32 + t * 4), hi - lo);
       } else {
-        const int lo = lw * npair / kMmaWarps, hi = (lw + 1) * npair / kMmaWarps;
+        const int lo = lw * npair / kWarpsPerGroup, hi = (lw + 1) * npair / kWarpsPerGroup;
         stage_fp16<NT, XS>(acc, sbase + lm_lane + lo * 32, xb, 2 * (c * (ck >> 2) + lo * 16 + t * 2), hi - lo);
       }
       __syncwarp();

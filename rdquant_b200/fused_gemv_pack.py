@@ -120,6 +120,41 @@ def pack_for_fused_gemv(layer_data: dict, splits: dict, k: int, device,
     return fd
 
 
+def fuse_layers(layers: list) -> tuple:
+    """Fuse linears that read the same input (q/k/v, gate/up) into one packed layer.
+
+    ``layers`` is a list of ``(layer_data, splits)`` with equal ``in_features``.  The fused
+    layer's output is the concatenation of the individual outputs in original channel
+    order; its rows are the individual rows regrouped NVFP4 | FP8 | FP16.  One launch then
+    streams all of them.  Returns ``(layer_data, splits)`` in checkpoint naming.
+    """
+    sizes = [[int(sp.get(f, 0)) for f in FORMAT_ORDER] for _, sp in layers]
+    tot = [sum(sz[g] for sz in sizes) for g in range(3)]
+    keys = (("weight_nvfp4", "weight_nvfp4_scale"), ("weight_fp8", "weight_fp8_scale"), ("weight_fp16",))
+    fused = {}
+    for g in range(3):
+        for key in keys[g]:
+            parts = [ld[key] for (ld, _), sz in zip(layers, sizes) if sz[g] > 0]
+            if parts:
+                fused[key] = torch.cat([p.reshape(p.shape[0], -1) if p.dim() > 1 else p for p in parts], dim=0)
+    inv_parts = []
+    base = [0, 0, 0]
+    for (ld, _), sz in zip(layers, sizes):
+        inv = ld["inv_permutation"].to(torch.int64)
+        n4, n8, _n16 = sz
+        pos = torch.where(inv < n4, inv + base[0],
+                          torch.where(inv < n4 + n8, inv - n4 + tot[0] + base[1], inv - n4 - n8 + tot[0] + tot[1] + base[2]))
+        inv_parts.append(pos)
+        base = [base[g] + sz[g] for g in range(3)]
+    fused["inv_permutation"] = torch.cat(inv_parts).to(torch.int32)
+    if any("bias" in ld for ld, _ in layers):
+        fused["bias"] = torch.cat([ld["bias"] if "bias" in ld else torch.zeros(sum(sz), dtype=torch.float16)
+                                   for (ld, _), sz in zip(layers, sizes)])
+    if "weight_nvfp4" in fused:
+        fused["nvfp4_global_scale"] = torch.ones(1)
+    return fused, dict(zip(FORMAT_ORDER, tot))
+
+
 def packed_weight_bytes(splits: dict, k: int) -> int:
     """Weight + scale bytes one GEMV launch must read: the roofline numerator."""
     n4, n8, n16 = (int(splits.get(f, 0)) for f in FORMAT_ORDER)
