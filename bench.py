@@ -188,6 +188,56 @@ def run_reference(args, rank: int, world: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_prefill(args, device, rank: int, world: int) -> None:
+    """Prefill GEMM (BASELINE configs[2]): the seven linears of the block at `--prefill` tokens."""
+    import torch
+
+    from rdquant_b200 import rdquant_cuda
+
+    m = args.prefill
+    steps, warmup = max(min(args.steps, 50), 1), max(args.warmup, 3)
+    units = build_block(device, seed=rank, copies=1, fuse=False)
+    gen = torch.Generator().manual_seed(99 + rank)
+    xs = [torch.randn(m, u["k"], generator=gen).half().to(device) for u in units]
+    flops = sum(2.0 * m * u["n"] * u["k"] for u in units)
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+
+    def one_step():
+        for x, u in zip(xs, units):
+            rdquant_cuda.mixed_gemm(x, u["fds"][0])
+
+    for _ in range(warmup):
+        one_step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    e0.record()
+    for _ in range(steps):
+        one_step()
+    e1.record()
+    e1.synchronize()
+    t1 = time.time()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop(t0, t1)
+    peaks, kind = measured_peaks()
+    tf = flops * steps / (ms * 1e-3) / 1e12
+    sustained = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+    line = {
+        "metric": "mixed_gemm_tflops", "value": tf * world, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16xf16->f32", "data": "synthetic",
+        "config": {"workload": f"qwen3-4b decoder block: 7 mixed-precision linears, prefill GEMM at M={m} tokens "
+                               "(BASELINE configs[2])", "l2_policy": "activations + outputs of a step exceed L2 for M >= 2048"},
+        "gpu_launches": steps * len(units),
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": sustained, "unit": "TFLOP/s", "frac": tf / sustained,
+                     "traffic": None, "peak_source": kind + " (sustained cuBLAS bf16)", "kernel": "gemm_mixed_kernel"},
+        "clocks": clocks,
+    }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -201,6 +251,8 @@ def main() -> None:
     ap.add_argument("--kernel", default="tiled", choices=["tiled", "stream", "generic"])
     ap.add_argument("--no-l2-prefetch", action="store_true")
     ap.add_argument("--no-fuse", action="store_true", help="seven launches per step instead of four")
+    ap.add_argument("--prefill", type=int, default=0, metavar="TOKENS",
+                    help="measure the tcgen05 prefill GEMM at this many tokens instead of the decode GEMV")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -224,6 +276,9 @@ def main() -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
+    if args.prefill > 0:
+        run_prefill(args, device, rank, world)
+        return
     steps, warmup, m = max(args.steps, 1), max(args.warmup, 3), args.m
     copies = max(args.copies, 2)
     layers = build_block(device, seed=rank, copies=copies, fuse=not args.no_fuse)

@@ -106,18 +106,23 @@ __device__ __forceinline__ void produce_fp16(GemmSmem &S, const GemmArgs &a, uin
   }
 }
 
+// MT = 128-token accumulators per CTA (1 or 2): with MT = 2 one dequantised weight stage
+// feeds two MMAs groups, halving the conversion work per flop.
+template <int MT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ GemmArgs a) {
+  constexpr int kStageAll = kStageA * MT;
+  constexpr uint32_t kCols = kTmemCols * MT;
   extern __shared__ uint8_t smem_raw[];
   __shared__ GemmSmem S;
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t a_base = (raw_addr + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
-  const uint32_t b_base = a_base + kStages * kStageA;
+  const uint32_t b_base = a_base + kStages * kStageAll;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int m0 = blockIdx.x * BM;
+  const int m0 = blockIdx.x * BM * MT;
   const int n0 = blockIdx.y * BN;
   const int N = a.n4 + a.n8 + a.n16;
   const int nkb = a.K / BK;
@@ -133,7 +138,7 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&S.tmem_base)),
-                 "r"(static_cast<uint32_t>(kTmemCols))
+                 "r"(kCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -186,8 +191,10 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
         if (kb >= kStages) alive = gemm_wait(&S.empty[s], ((kb / kStages) - 1) & 1, &S.abort_flag);
         if (!alive) break;
         const uint32_t full = smem_u32(&S.full[s]);
-        mbar_arrive_expect_tx(full, kStageA);
-        tma_load_2d(a_base + s * kStageA, &xmap, kb * BK, m0, full);
+        mbar_arrive_expect_tx(full, kStageAll);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+          tma_load_2d(a_base + s * kStageAll + mt * kStageA, &xmap, kb * BK, m0 + mt * BM, full);
       }
     }
   } else if (warp == 1) {
@@ -200,10 +207,14 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
         alive = gemm_wait(&S.full[s], (kb / kStages) & 1, &S.abort_flag);
         if (!alive) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t da = make_desc_sw128(a_base + s * kStageA);
         const uint64_t db = make_desc_sw128(b_base + s * kStageB);
 #pragma unroll
-        for (int k4 = 0; k4 < BK / 16; ++k4) umma_f16(tmem, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0 ? 1u : 0u);
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint64_t da = make_desc_sw128(a_base + s * kStageAll + mt * kStageA);
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4)
+            umma_f16(tmem + mt * kTmemCols, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0 ? 1u : 0u);
+        }
         umma_commit(smem_u32(&S.empty[s]));
       }
       umma_commit(smem_u32(&S.accum));
@@ -233,12 +244,13 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
       const bool ok = gemm_wait(&S.accum, 0, &S.abort_flag);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int q = warp & 3;  // tensor-memory lane quarter this warp may read
-      const int m = m0 + q * 32 + lane;
       if (ok) {
 #pragma unroll 1
-        for (int cc = 0; cc < BN / 32; ++cc) {
+        for (int ci = 0; ci < MT * (BN / 32); ++ci) {
+          const int mt = ci / (BN / 32), cc = ci % (BN / 32);
+          const int m = m0 + mt * BM + q * 32 + lane;
           uint32_t r[32];
-          tmem_ld32(tmem + (static_cast<uint32_t>(q * 32) << 16) + cc * 32, r);
+          tmem_ld32(tmem + (static_cast<uint32_t>(q * 32) << 16) + mt * kTmemCols + cc * 32, r);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           if (m < a.M) {
             __half *dst = a.y + 1ll * m * N + n0 + cc * 32;
@@ -271,7 +283,7 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(static_cast<uint32_t>(kTmemCols))
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kCols)
                  : "memory");
   }
   if (tid == 0 && S.abort_flag) atomicAdd(&g_gemm_aborts, 1);
@@ -295,9 +307,11 @@ int launch_gemm(const GemmArgs &a, cudaStream_t stream) {
   static bool attr_done[64] = {};
   int dev = 0;
   RDQ_CUDA(cudaGetDevice(&dev));
-  const int smem = kStages * (kStageA + kStageB) + 1024;
+  const int smem1 = kStages * (kStageA + kStageB) + 1024;
+  const int smem2 = kStages * (2 * kStageA + kStageB) + 1024;
   if (dev < 64 && !attr_done[dev]) {
-    RDQ_CUDA(cudaFuncSetAttribute(gemm_mixed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    RDQ_CUDA(cudaFuncSetAttribute(gemm_mixed_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1));
+    RDQ_CUDA(cudaFuncSetAttribute(gemm_mixed_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
     attr_done[dev] = true;
   }
   const int N = a.n4 + a.n8 + a.n16;
@@ -310,8 +324,16 @@ int launch_gemm(const GemmArgs &a, cudaStream_t stream) {
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   RDQ_REQUIRE(rc == CUDA_SUCCESS, RDQ_E_CUDA, "cuTensorMapEncodeTiled failed with code %d", static_cast<int>(rc));
-  const dim3 grid((a.M + BM - 1) / BM, (N + BN - 1) / BN);
-  gemm_mixed_kernel<<<grid, kGemmThreads, smem, stream>>>(xmap, a);
+  // 256-token tiles once there are enough of them to fill the GPU
+  const int ntile_n = (N + BN - 1) / BN;
+  const bool two = ((a.M + 2 * BM - 1) / (2 * BM)) * ntile_n >= sm_count();
+  if (two) {
+    const dim3 grid((a.M + 2 * BM - 1) / (2 * BM), ntile_n);
+    gemm_mixed_kernel<2><<<grid, kGemmThreads, smem2, stream>>>(xmap, a);
+  } else {
+    const dim3 grid((a.M + BM - 1) / BM, ntile_n);
+    gemm_mixed_kernel<1><<<grid, kGemmThreads, smem1, stream>>>(xmap, a);
+  }
   RDQ_CUDA(cudaGetLastError());
   return RDQ_OK;
 }

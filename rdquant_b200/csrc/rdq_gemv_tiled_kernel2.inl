@@ -403,7 +403,7 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
   }
 
 #ifdef RDQ_TIMELINE
-  long long cyc_wait = 0, cyc_comp = 0, cyc_flush = 0, tprev = clock64();
+  long long cyc_wait = 0, cyc_comp = 0, cyc_flush = 0, cyc_flwait = 0, cyc_flwrite = 0, tprev = clock64();
   if (warp == 0) TTL_MARK(15);
 #define TTL_LAP(acc_) do { const long long tnow_ = clock64(); acc_ += tnow_ - tprev; tprev = tnow_; } while (0)
 #else
@@ -448,10 +448,12 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
 
     // ---- hand the partial sums of this segment to the epilogue warp
     const int fslot = q % kFR;
+    TTL_LAP(cyc_flush);
     if (q >= kFR && !mbar_wait(smem_u32(&fl_empty[fslot]), ((q / kFR) - 1) & 1)) {
       if (lane == 0) atomicExch(status, 5);
       return;
     }
+    TTL_LAP(cyc_flwait);
     float *buf = flush + fslot * kSlotFloats;
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
@@ -466,6 +468,7 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(smem_u32(&fl_full[fslot]));
+    TTL_LAP(cyc_flwrite);
   }
 #ifdef RDQ_TIMELINE
   if (warp == 0 && lane == 0 && blockIdx.x < 148) {
@@ -474,6 +477,9 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
     g_ttimeline[g_tl_base + blockIdx.x * 32 + 17] = cyc_comp;
     g_ttimeline[g_tl_base + blockIdx.x * 32 + 18] = cyc_flush;
     g_ttimeline[g_tl_base + blockIdx.x * 32 + 19] = it;
+    g_ttimeline[g_tl_base + blockIdx.x * 32 + 12] = cyc_flwait;
+    g_ttimeline[g_tl_base + blockIdx.x * 32 + 13] = cyc_flwrite;
+    g_ttimeline[g_tl_base + blockIdx.x * 32 + 14] = nseg;
   }
 #endif
 }
