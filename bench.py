@@ -334,35 +334,31 @@ def main() -> None:
     ms = e0.elapsed_time(e1)
     status_bad = sum(int(fd["tile_counters"].abs().sum().item()) for l in layers for fd in l["fds"])
 
-    # ---- end to end through the public module call, host buffers in, host buffers out
-    from rdquant_b200.inference import FusedMixedLinear
+    # ---- end to end through the public API, host buffers in, host buffers out
+    from rdquant_b200.inference import FusedMixedLinear, GraphedDecodeStep
 
-    mods = []
-    for l in layers:
-        fd = l["fds"][0]
-        mod = FusedMixedLinear(n_nvfp4=fd["n_fp4"], n_fp8=fd["n_fp8"], n_fp16=fd["n_fp16"], k=l["k"],
-                               inv_perm=fd["inv_perm"], bias=None, marlin_data=None, fused_data=fd)
-        mod.use_pdl = not args.no_pdl
-        mods.append(mod)
-    x_host = [x.cpu().pin_memory() for x in xs]
-    y_host = [torch.empty(m, l["n"], dtype=torch.float16).pin_memory() for l in layers]
-    x_dev = [torch.empty_like(x) for x in xs]
+    def modules_of(copy: int):
+        out = []
+        for l in layers:
+            fd = l["fds"][copy]
+            out.append(FusedMixedLinear(n_nvfp4=fd["n_fp4"], n_fp8=fd["n_fp8"], n_fp16=fd["n_fp16"], k=l["k"],
+                                        inv_perm=fd["inv_perm"], bias=None, marlin_data=None, fused_data=fd))
+        return out
+
+    # one graphed step per weight copy, rotated like the device-only measurement
+    runners = [GraphedDecodeStep(modules_of(c), m=m, use_pdl=not args.no_pdl) for c in range(copies)]
+    for runner in runners:
+        for xh, x in zip(runner.x_host, xs):
+            xh.copy_(x.cpu())
     e2e_steps = min(steps, 200)
-
-    def e2e_step() -> None:
-        for li, mod in enumerate(mods):
-            x_dev[li].copy_(x_host[li], non_blocking=True)
-            y = mod(x_dev[li])
-            y_host[li].copy_(y, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-
-    for _ in range(3):
-        e2e_step()
+    for i in range(copies):
+        runners[i].run()
     if world > 1:
         dist.barrier()
     te0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
+    for i in range(e2e_steps):
+        # host activations in, host results out: one graph replay (H2D copies, GEMVs, D2H copies)
+        runners[i % copies].run()
     te = time.perf_counter() - te0
     clocks = sampler.stop(t0, t1)
 
@@ -378,6 +374,9 @@ def main() -> None:
     launches = steps * len(layers)
     per_launch_bytes = step_bytes / len(layers)
     achieved = per_launch_bytes / (ms * 1e-3 / launches) / 1e9
+    # dram__bytes_read + dram__bytes_write per launch from the ncu capture summarised in
+    # profiles/gemv_tiled_block_m1.md (average over the four fused launches of a step)
+    traffic = 19.85e6 if (m == 1 and not args.no_fuse and args.kernel == "tiled") else None
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -396,13 +395,13 @@ def main() -> None:
         },
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peak_kind,
+                     "frac": achieved / peaks["hbm_gbs"], "traffic": traffic, "peak_source": peak_kind,
                      "frac_of_nominal_8tbs": achieved / 8000.0, "kernel": "gemv_%s_kernel" % args.kernel,
                      "bytes_per_launch": per_launch_bytes},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": sum(2 * m * l["k"] for l in layers),
                 "d2h_bytes_per_step": sum(2 * m * l["n"] for l in layers), "steps": e2e_steps,
                 "ms_per_step": 1e3 * te / e2e_steps,
-                "api": "FusedMixedLinear.forward per layer, pinned host x -> device, y -> pinned host, sync per step"},
+                "api": "inference.GraphedDecodeStep.run(): pinned host x -> device, fused GEMVs, y -> pinned host as one CUDA-graph replay, synchronised every step; weight copies rotate as in the device-only measurement"},
         "clocks": clocks,
         "status_words_nonzero": status_bad,
     }

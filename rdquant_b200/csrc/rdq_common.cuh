@@ -140,6 +140,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity, uint32_t
 // Bounded wait: gives up after `limit` suspended waits of up to 0.1 ms each (about a
 // second) and reports false, so a lost copy or a logic error cannot hang the device.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = 10000u) {
+#pragma unroll 1
   for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try(bar, parity, 100000u)) return true;
   }

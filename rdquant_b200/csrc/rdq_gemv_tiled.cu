@@ -11,7 +11,8 @@
 // of 16 B, so ldmatrix reads of 8 rows never collide on a bank.
 //
 // Kernel: images are numbered in storage order and each CTA takes a contiguous,
-// byte-balanced range of them.  Inside a CTA
+// cost-balanced range of them (an NVFP4 image costs more instructions than an FP8 or FP16
+// image of the same size).  Inside a CTA
 //   producer warp   one cp.async.bulk (TMA) copy per image (12-19 KB) into a
 //                   shared-memory ring, mbarrier tracked.  It starts BEFORE
 //                   griddepcontrol.wait: under programmatic dependent launch the
@@ -37,6 +38,8 @@
 //
 // Reference behaviour replaced: the Marlin-repacked split-K family K2-K7 of
 // rdquant/csrc/fused_gemv.cu (:1244-1969; repack rdquant/fused_gemv_pack.py:151-172).
+#include <cstdlib>
+
 #include "rdq_kernels.cuh"
 
 namespace rdq {
@@ -49,7 +52,7 @@ constexpr int kGroups = 3;          // warp groups; stage i is consumed by group
 constexpr int kWarpsPerGroup = 4;   // power of two
 static_assert(kGroups * kWarpsPerGroup == kMmaWarps, "warp groups must cover the MMA warps");
 constexpr int kThreads = (kMmaWarps + 2) * 32;  // + producer warp + epilogue warp
-constexpr int kFlushRing = 4;
+constexpr int kFlushRing = 8;  // deepest flush ring
 constexpr int kMetaSegs = 32;
 constexpr int kMaxStages = 12;
 

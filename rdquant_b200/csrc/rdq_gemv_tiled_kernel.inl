@@ -9,18 +9,21 @@ struct TSched {
   int S4, S8, S16;   // images per tile in each group
   int t4, t8;        // tiles in the NVFP4 / FP8 groups
   int e4, e8, e16;   // end of each group's image range
-  int u4, u8;        // image weight (bytes / 16) of NVFP4 / other images
+  int u4, u8, u16;   // scheduling cost of one NVFP4 / FP8 / FP16 image
+  int img4, img8;    // image bytes (FP8 and FP16 images have the same size)
   long long w4, w8, W;
   int G;
 
   __device__ __forceinline__ int image_of_pos(long long p) const {
     if (p < w4) return static_cast<int>(p / u4);
-    if (p < W) return e4 + static_cast<int>((p - w4) / u8);
+    if (p < w8) return e4 + static_cast<int>((p - w4) / u8);
+    if (p < W) return e8 + static_cast<int>((p - w8) / u16);
     return e16;
   }
   __device__ __forceinline__ long long pos_of_image(int s) const {
     if (s < e4) return 1ll * s * u4;
-    return w4 + 1ll * (s - e4) * u8;
+    if (s < e8) return w4 + 1ll * (s - e4) * u8;
+    return w8 + 1ll * (s - e8) * u16;
   }
   __device__ __forceinline__ int boundary(int b) const {
     if (b >= G) return e16;
@@ -40,7 +43,8 @@ struct TSched {
   }
   // byte offset of image s inside the tiled buffer
   __device__ __forceinline__ long long image_offset(int s) const {
-    return pos_of_image(s) << 4;
+    if (s < e4) return 1ll * s * img4;
+    return 1ll * e4 * img4 + 1ll * (s - e4) * img8;
   }
 };
 
@@ -127,6 +131,7 @@ struct TiledArgs {
   int status_idx;
   int nstages;
   int slot_bytes;
+  int flush_depth;
 };
 
 #ifdef RDQ_TIMELINE
@@ -139,7 +144,12 @@ __device__ __forceinline__ void ttl_mark_(int slot, int ttl_m) {
   if (blockIdx.x < 148 && slot < 32) g_ttimeline[g_tl_base + blockIdx.x * 32 + slot] = t;
 }
 #define TTL_MARK(slot) do { if ((threadIdx.x & 31) == 0) ttl_mark_(slot, a.M); } while (0)
+// fine-grained per-stage clocks of two CTAs of the M == 3 launch
+__device__ long long g_tstage[2 * 48 * 8];
+#define TST(idx_, col_) do { if (a.n4 + a.n8 + a.n16 > 15000 && (blockIdx.x == 10 || blockIdx.x == 100) && (idx_) < 48) \
+  g_tstage[((blockIdx.x == 100) * 48 + (idx_)) * 8 + (col_)] = clock64(); } while (0)
 #else
+#define TST(idx_, col_) do { } while (0)
 #define TTL_MARK(slot) do { } while (0)
 #endif
 

@@ -3,6 +3,11 @@ namespace rdq {
 
 namespace {
 
+#ifndef RDQ_STAGE_UNROLL
+#define RDQ_STAGE_UNROLL 2
+#endif
+constexpr int kStageUnroll = RDQ_STAGE_UNROLL;  // pair-loop unrolling of the NVFP4 / FP8 stages
+
 // Activation fragment loads: from the shared-memory copy (XS) or from global memory.
 // `base` is a shared-memory byte address (XS) or a generic pointer value.
 template <bool XS>
@@ -71,6 +76,7 @@ template <int NT, bool XS>
 __device__ __forceinline__ void stage_fp4(float (&acc)[NT][2][4], uint32_t lm_addr, uint32_t sc_addr,
                                           uint32_t sc8_addr, const uint64_t (&xb)[NT], int xoff, int npairs,
                                           uint32_t sel) {
+#pragma unroll kStageUnroll
   for (int i = 0; i < npairs; ++i) {
     uint32_t w[4];
     ldmatrix_x4(lm_addr, w[0], w[1], w[2], w[3]);
@@ -95,6 +101,7 @@ __device__ __forceinline__ void stage_fp4(float (&acc)[NT][2][4], uint32_t lm_ad
 template <int NT, bool XS>
 __device__ __forceinline__ void stage_fp8(float (&acc)[NT][2][4], uint32_t lm_addr, const uint64_t (&xb)[NT],
                                           int xoff, int npairs) {
+#pragma unroll kStageUnroll
   for (int i = 0; i < npairs; ++i) {
     uint32_t w[4];
     ldmatrix_x4(lm_addr, w[0], w[1], w[2], w[3]);
@@ -123,27 +130,31 @@ __device__ __forceinline__ void stage_fp8(float (&acc)[NT][2][4], uint32_t lm_ad
 template <int NT, bool XS>
 __device__ __forceinline__ void stage_fp16(float (&acc)[NT][2][4], uint32_t lm_addr, const uint64_t (&xb)[NT],
                                            int xoff, int npairs) {
-  for (int i = 0; i < npairs; ++i) {
+  auto one = [&](int c) {
     uint32_t w[4];
     ldmatrix_x4(lm_addr, w[0], w[1], w[2], w[3]);
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
       const uint32_t x0 = ldx4<XS>(xb[n], xoff);
       const uint32_t x1 = ldx4<XS>(xb[n], xoff + 16);
-      mma_16816(acc[n][i & 1], w[0], w[1], w[2], w[3], x0, x1);
+      mma_16816(acc[n][c], w[0], w[1], w[2], w[3], x0, x1);
     }
     lm_addr += 32;
     xoff += 32;
+  };
+  int i = 0;
+#pragma unroll 1
+  for (; i + 1 < npairs; i += 2) {
+    one(0);
+    one(1);
   }
+  if (i < npairs) one(0);
 }
 
 // NT = number of 8-row activation groups (1: M <= 8, 2: M <= 16)
 template <int NT, bool XS>
 __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledArgs a,
                                                   const __grid_constant__ TSched sc) {
-  constexpr int kMp = 8 * NT;
-  constexpr int kFR = kFlushRing / NT;  // flush ring depth
-  constexpr int kSlotFloats = kMmaWarps * kTileRows * kMp;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t bar_full[kMaxStages];
   __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
@@ -157,15 +168,20 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
   const int K = a.K, M = a.M;
   const int N = a.n4 + a.n8 + a.n16;
   const int nst = a.nstages;
+  // flush ring: fdepth slots of [12 warps][16 rows][mp activation rows] partial sums
+  const int mp = M, fdepth = a.flush_depth;
+  const int slot_floats = kMmaWarps * kTileRows * mp;
   float *flush = reinterpret_cast<float *>(smem + nst * a.slot_bytes);
-  int *meta_col = reinterpret_cast<int *>(flush + kFR * kSlotFloats);
+  int *meta_col = reinterpret_cast<int *>(flush + fdepth * slot_floats);
   float *meta_scl = reinterpret_cast<float *>(meta_col + kMetaSegs * kTileRows);
   float *meta_bia = meta_scl + kMetaSegs * kTileRows;
   uint8_t *xsm = reinterpret_cast<uint8_t *>(meta_bia + kMetaSegs * kTileRows);
   const int xpitch = 2 * a.K + 16;  // activation row pitch in shared memory: skewed against bank conflicts
 
-  const int s_begin = sc.boundary(blockIdx.x);
-  const int s_end = sc.boundary(blockIdx.x + 1);
+  // lane L holds the first image of CTA bx + L (one call site for the 64-bit divisions)
+  const int bnd = sc.boundary(static_cast<int>(blockIdx.x) + lane);
+  const int s_begin = __shfl_sync(0xffffffffu, bnd, 0);
+  const int s_end = __shfl_sync(0xffffffffu, bnd, 1);
   const int first_tile = (s_end > s_begin) ? sc.tile_of_image(s_begin) : 0;
   const int nseg = (s_end > s_begin) ? (sc.tile_of_image(s_end - 1) - first_tile + 1) : 0;
   int32_t *status = a.flags + a.status_idx;
@@ -178,7 +194,7 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
       mbar_init(smem_u32(&bar_full[i]), 1);
       mbar_init(smem_u32(&bar_empty[i]), kWarpsPerGroup);
     }
-    for (int i = 0; i < kFR; ++i) {
+    for (int i = 0; i < fdepth; ++i) {
       mbar_init(smem_u32(&fl_full[i]), kMmaWarps);
       mbar_init(smem_u32(&fl_empty[i]), 1);
     }
@@ -201,11 +217,15 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
     auto send_x = [&]() {
       if (x_sent) return;
       x_sent = true;
+      // Only this thread executes the grid-dependency wait; every other warp of the CTA
+      // sleeps on bar_x, which completes after it (and after the activation copies).
       pdl_wait();
+      const uint32_t bx = smem_u32(&bar_x);
       if (XS) {
-        const uint32_t bx = smem_u32(&bar_x);
         mbar_arrive_expect_tx(bx, static_cast<uint32_t>(M) * 2u * K);
         for (int m = 0; m < M; ++m) bulk_g2s(smem_u32(xsm) + m * xpitch, a.x + 1ll * m * K, 2u * K, bx);
+      } else {
+        mbar_arrive(bx);
       }
     };
     int it = 0, slot = 0, round = 0;
@@ -221,6 +241,7 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
           }
         }
         const uint32_t full = smem_u32(&bar_full[slot]);
+        TST(it, 0);
         mbar_arrive_expect_tx(full, bytes);
         bulk_g2s(smem_base + slot * a.slot_bytes, a.tiled + sc.image_offset(sg.first_img + c), bytes, full);
         if (++slot == nst) { slot = 0; ++round; }
@@ -230,6 +251,20 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
     return;
   }
 
+#ifdef RDQ_TIMELINE
+  if (warp == kMmaWarps + 2) {
+    // debug only: records when each stage's bytes have landed
+    if (lane != 0) return;
+    int nimg = s_end - s_begin;
+    for (int it = 0, slot = 0, round = 0; it < nimg; ++it) {
+      bool ok = false;
+      for (int spin = 0; spin < 4000000 && !ok; ++spin) ok = mbar_try(smem_u32(&bar_full[slot]), round & 1, 0u);
+      TST(it, 7);
+      if (++slot == nst) { slot = 0; ++round; }
+    }
+    return;
+  }
+#endif
   if (warp == kMmaWarps + 1) {
     // ================================================================ epilogue warp
     // output column, scale and bias of every row this CTA finishes: constants of the
@@ -264,94 +299,84 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
     }
     __syncwarp();
     TTL_MARK(1);
-    pdl_wait();  // y, workspace and flags belong to this launch only after the wait
+    // y, workspace and flags belong to this launch only once the preceding grid is done
+    if (!mbar_wait(smem_u32(&bar_x), 0)) {
+      if (lane == 0) atomicExch(status, 6);
+      return;
+    }
     TTL_MARK(2);
+    // lane = (row, half): each half sums six of the twelve partials of its row
     const int row = lane & 15;
-    const int mh = lane >> 4;
-    const int mper = (M + 1) >> 1;
-    const int m_lo = mh * mper;
-    const int m_hi = min(M, m_lo + mper);
+    const int half = lane >> 4;
+    int fslot = 0, fround = 0;
+#pragma unroll 1
     for (int q = 0; q < nseg; ++q) {
       const int idx = tseg_order(q, nseg);
       const TSeg sg = tseg_at(sc, s_begin, s_end, first_tile + idx);
-      const int slot = q % kFR;
-      if (!mbar_wait(smem_u32(&fl_full[slot]), (q / kFR) & 1)) {
+      if (!mbar_wait(smem_u32(&fl_full[fslot]), fround & 1)) {
         if (lane == 0) atomicExch(status, 2);
         return;
       }
-      const float *buf = flush + slot * kSlotFloats;
-      float sum[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int m = m_lo + i;
+      if (lane == 0) TST(q, 5);
+      const float *buf = flush + fslot * slot_floats + (half * (kMmaWarps / 2) * kTileRows + row) * mp;
+      int col;
+      float scl, bia;
+      if (idx < kMetaSegs) {
+        col = meta_col[idx * kTileRows + row];
+        scl = meta_scl[idx * kTileRows + row];
+        bia = meta_bia[idx * kTileRows + row];
+      } else {
+        const int prow = sg.gtile * kTileRows + row;
+        col = a.perm ? a.perm[prow] : prow;
+        scl = (sg.fmt == 1) ? a.s8[prow - a.n4] : (sg.fmt == 0 ? a.global4 : 1.f);
+        bia = a.bias ? __half2float(a.bias[col]) : 0.f;
+      }
+      // split tile whose first image this CTA holds: the other parts come from the CTAs
+      // bx + 1 .. b_last, in that order
+      int b_last = blockIdx.x;
+      if (sg.starts && !sg.ends) {
+        const int s_last = sg.first_img + sg.S - 1;
+        b_last += __popc(__ballot_sync(0xffffffffu, lane >= 1 && bnd <= s_last && bnd < sc.e16));
+        if (lane == 0 && b_last >= static_cast<int>(blockIdx.x) + 31) atomicExch(status, 7);
+      }
+      float *ws = a.workspace + 1ll * blockIdx.x * 256 + row * 16;
+      bool ok = true;
+#pragma unroll 1
+      for (int m = 0; m < M; ++m) {
         float v = 0.f;
-        if (m < m_hi) {
 #pragma unroll
-          for (int w = 0; w < kMmaWarps; ++w) v += buf[(w * kTileRows + row) * kMp + m];
+        for (int w = 0; w < kMmaWarps / 2; ++w) v += buf[w * kTileRows * mp + m];
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        if (half) continue;
+        if (!sg.starts) {
+          // continuation of a tile another CTA started: store the partial sums into this
+          // CTA's workspace slot (idle words read 0xffffffff); the owner polls them
+          ws[m] = v;
+          continue;
         }
-        sum[i] = v;
+#pragma unroll 1
+        for (int b = blockIdx.x + 1; b <= b_last; ++b) {
+          float *pw = a.workspace + 1ll * b * 256 + row * 16 + m;
+          uint32_t bits = 0xffffffffu;
+#pragma unroll 1
+          for (int spin = 0; spin < 2000000 && bits == 0xffffffffu; ++spin) {
+            asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(bits) : "l"(pw) : "memory");
+            if (bits == 0xffffffffu) __nanosleep(200);
+          }
+          if (bits == 0xffffffffu) ok = false;
+          v += __uint_as_float(bits);
+          *pw = __uint_as_float(0xffffffffu);  // slot idle again
+        }
+        a.y[1ll * m * N + col] = __float2half_rn(fmaf(v, scl, bia));
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&fl_empty[slot]));
-
-      if (!sg.starts) {
-        // continuation of a tile another CTA started: store the partial sums into this
-        // CTA's workspace slot (idle words read 0xffffffff); the owner polls them
-        float *ws = a.workspace + 1ll * blockIdx.x * 256;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int m = m_lo + i;
-          if (m < m_hi) ws[row * 16 + m] = sum[i];
-        }
-        TTL_MARK(20 + (q < 10 ? q : 10));
-        continue;
+      if (lane == 0) mbar_arrive(smem_u32(&fl_empty[fslot]));
+      if (++fslot == fdepth) { fslot = 0; ++fround; }
+      if (__any_sync(0xffffffffu, !ok)) {
+        if (lane == 0) atomicExch(status, 3);
+        return;
       }
-      if (!sg.ends) {
-        // this CTA holds the first image of a split tile: collect the other parts in CTA order
-        const int b_last = sc.cta_of_image(sg.first_img + sg.S - 1);
-        bool ok = true;
-        for (int b = blockIdx.x + 1; b <= b_last; ++b) {
-          float *pw = a.workspace + 1ll * b * 256;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int m = m_lo + i;
-            if (m < m_hi) {
-              uint32_t bits = 0xffffffffu;
-              for (int spin = 0; spin < 2000000 && bits == 0xffffffffu; ++spin) {
-                asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(bits) : "l"(pw + row * 16 + m) : "memory");
-                if (bits == 0xffffffffu) __nanosleep(200);
-              }
-              if (bits == 0xffffffffu) ok = false;
-              sum[i] += __uint_as_float(bits);
-              pw[row * 16 + m] = __uint_as_float(0xffffffffu);  // slot idle again
-            }
-          }
-        }
-        if (__any_sync(0xffffffffu, !ok)) {
-          if (lane == 0) atomicExch(status, 3);
-          return;
-        }
-      }
-      {
-        int col;
-        float scl, bia;
-        if (idx < kMetaSegs) {
-          col = meta_col[idx * kTileRows + row];
-          scl = meta_scl[idx * kTileRows + row];
-          bia = meta_bia[idx * kTileRows + row];
-        } else {
-          const int prow = sg.gtile * kTileRows + row;
-          col = a.perm ? a.perm[prow] : prow;
-          scl = (sg.fmt == 1) ? a.s8[prow - a.n4] : (sg.fmt == 0 ? a.global4 : 1.f);
-          bia = a.bias ? __half2float(a.bias[col]) : 0.f;
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int m = m_lo + i;
-          if (m < m_hi) a.y[1ll * m * N + col] = __float2half_rn(fmaf(sum[i], scl, bia));
-        }
-      }
-      TTL_MARK(20 + (q < 10 ? q : 10));
+      if (lane == 0) TST(q, 6);
     }
     TTL_MARK(31);
     return;
@@ -377,41 +402,35 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[n][c][i] = 0.f;
 
-  // x is produced by the preceding kernel: do not touch it before this.
-  pdl_wait();
+  // x is produced by the preceding kernel: do not touch it before the producer thread has
+  // seen that kernel complete (and, with XS, has copied the rows into shared memory).
+  if (!mbar_wait(smem_u32(&bar_x), 0)) {
+    if (lane == 0) atomicExch(status, 6);
+    return;
+  }
   if (warp == 0) TTL_MARK(3);
-
   // Lanes of activation rows >= M read row 0 instead: their output columns are never stored.
   uint64_t xb[NT];
-  if (XS) {
-    // the producer thread copies the activation rows into shared memory (bulk copies)
-    if (!mbar_wait(smem_u32(&bar_x), 0)) {
-      if (lane == 0) atomicExch(status, 6);
-      return;
-    }
 #pragma unroll
-    for (int n = 0; n < NT; ++n) {
-      const int m = n * 8 + g;
-      xb[n] = smem_u32(xsm) + (m < M ? m : 0) * xpitch;
-    }
-  } else {
-#pragma unroll
-    for (int n = 0; n < NT; ++n) {
-      const int m = n * 8 + g;
-      xb[n] = reinterpret_cast<uint64_t>(a.x + 1ll * (m < M ? m : 0) * K);
-    }
+  for (int n = 0; n < NT; ++n) {
+    const int m = n * 8 + g;
+    xb[n] = XS ? static_cast<uint64_t>(smem_u32(xsm) + (m < M ? m : 0) * xpitch)
+               : reinterpret_cast<uint64_t>(a.x + 1ll * (m < M ? m : 0) * K);
   }
 
 #ifdef RDQ_TIMELINE
-  long long cyc_wait = 0, cyc_comp = 0, cyc_flush = 0, cyc_flwait = 0, cyc_flwrite = 0, tprev = clock64();
+  long long cyc_wait = 0, cyc_comp = 0, cyc_flush = 0, cyc_o2 = 0, cyc_flwait = 0, cyc_flwrite = 0, tprev = clock64();
   if (warp == 0) TTL_MARK(15);
+  if (warp == 0 && lane == 0) TST(47, 7);
 #define TTL_LAP(acc_) do { const long long tnow_ = clock64(); acc_ += tnow_ - tprev; tprev = tnow_; } while (0)
 #else
 #define TTL_LAP(acc_) do { } while (0)
 #endif
-  int it = 0, slot = 0, round = 0;
+  int it = 0, slot = 0, round = 0, fslot = 0, fround = 0;
+#pragma unroll 1
   for (int q = 0; q < nseg; ++q) {
     const TSeg sg = tseg_at(sc, s_begin, s_end, first_tile + tseg_order(q, nseg));
+#pragma unroll 1
     for (int c = sg.c0; c < sg.c1; ++c, ++it) {
       // stages go round robin to the warp groups: a warp then has a whole quarter of a stage
       // to work on per barrier wait
@@ -425,6 +444,7 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
         return;
       }
       TTL_LAP(cyc_wait);
+      if (wq == 0 && lane == 0) TST(it, 1);
       const uint32_t sbase = smem_base + slot * a.slot_bytes;
       // inside a group the warps take turns on the pair ranges, so uneven splits average out
       const int lw = (wq + it / kGroups) & (kWarpsPerGroup - 1);
@@ -443,35 +463,38 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
       if (lane == 0) mbar_arrive(smem_u32(&bar_empty[slot]));
       if (++slot == nst) { slot = 0; ++round; }
       TTL_LAP(cyc_comp);
+      if (wq == 0 && lane == 0) TST(it, 2);
     }
-    if (warp == 0) TTL_MARK(4 + (q < 10 ? q : 10));
+    if (warp == 0 && q == 0) TTL_MARK(4);
 
     // ---- hand the partial sums of this segment to the epilogue warp
-    const int fslot = q % kFR;
-    TTL_LAP(cyc_flush);
-    if (q >= kFR && !mbar_wait(smem_u32(&fl_empty[fslot]), ((q / kFR) - 1) & 1)) {
+    TTL_LAP(cyc_o2);
+    if (lane == 0 && warp == 0) TST(q, 3);
+    if (fround > 0 && !mbar_wait(smem_u32(&fl_empty[fslot]), (fround - 1) & 1)) {
       if (lane == 0) atomicExch(status, 5);
       return;
     }
     TTL_LAP(cyc_flwait);
-    float *buf = flush + fslot * kSlotFloats;
+    float *buf = flush + fslot * slot_floats + warp * kTileRows * mp;
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int r = g + (i >> 1) * 8;
         const int m = n * 8 + 2 * t + (i & 1);
-        if (m < M) buf[(warp * kTileRows + r) * kMp + m] = acc[n][0][i] + acc[n][1][i];
+        if (m < M) buf[r * mp + m] = acc[n][0][i] + acc[n][1][i];
         acc[n][0][i] = 0.f;
         acc[n][1][i] = 0.f;
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(smem_u32(&fl_full[fslot]));
+    if (++fslot == fdepth) { fslot = 0; ++fround; }
     TTL_LAP(cyc_flwrite);
+    if (lane == 0 && warp == 0) TST(q, 4);
   }
 #ifdef RDQ_TIMELINE
-  if (warp == 0 && lane == 0 && blockIdx.x < 148) {
+  if (warp == 5 && lane == 0 && blockIdx.x < 148) {
     const int ttl_m = a.M;
     g_ttimeline[g_tl_base + blockIdx.x * 32 + 16] = cyc_wait;
     g_ttimeline[g_tl_base + blockIdx.x * 32 + 17] = cyc_comp;
@@ -480,6 +503,7 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
     g_ttimeline[g_tl_base + blockIdx.x * 32 + 12] = cyc_flwait;
     g_ttimeline[g_tl_base + blockIdx.x * 32 + 13] = cyc_flwrite;
     g_ttimeline[g_tl_base + blockIdx.x * 32 + 14] = nseg;
+    g_ttimeline[g_tl_base + blockIdx.x * 32 + 11] = cyc_o2;
   }
 #endif
 }
@@ -489,6 +513,9 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
 #ifdef RDQ_TIMELINE
 extern "C" int rdq_debug_timeline_tiled(long long *host_out) {
   return cudaMemcpyFromSymbol(host_out, g_ttimeline, sizeof(long long) * 4 * 148 * 32) == cudaSuccess ? 0 : -3;
+}
+extern "C" int rdq_debug_tstage(long long *host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_tstage, sizeof(long long) * 2 * 48 * 8) == cudaSuccess ? 0 : -3;
 }
 #endif
 
@@ -511,15 +538,32 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
   sc.e4 = sc.t4 * sc.S4;
   sc.e8 = sc.e4 + sc.t8 * sc.S8;
   sc.e16 = sc.e8 + t16 * sc.S16;
-  sc.u4 = img_bytes(0, ck) / 16;
-  sc.u8 = img_bytes(1, ck) / 16;
+  // Images are balanced by what they cost an SM, not by their bytes: the kernel is bound by
+  // instruction issue, and a 16 x ck NVFP4 image (conversion + block scaling) costs more
+  // than an FP8 or FP16 image of the same size (weights chosen by measurement).
+  sc.u4 = 10;
+  sc.u8 = 6;
+  sc.u16 = 5;
+  if (const char *env = getenv("RDQ_TILED_COST")) {  // A/B knob: "u4,u8,u16"
+    int c4 = 0, c8 = 0, c16 = 0;
+    if (sscanf(env, "%d,%d,%d", &c4, &c8, &c16) == 3 && c4 >= c8 && c8 >= c16 && c16 >= 1 && c4 <= 4096) {
+      sc.u4 = c4; sc.u8 = c8; sc.u16 = c16;
+    }
+  }
+  sc.img4 = img_bytes(0, ck);
+  sc.img8 = img_bytes(1, ck);
   sc.w4 = 1ll * sc.e4 * sc.u4;
   sc.w8 = sc.w4 + 1ll * (sc.e8 - sc.e4) * sc.u8;
-  sc.W = sc.w8 + 1ll * (sc.e16 - sc.e8) * sc.u8;
+  sc.W = sc.w8 + 1ll * (sc.e16 - sc.e8) * sc.u16;
   // every CTA must own at least one image: its share may not be shorter than the
   // heaviest image
   int G = sm_count();
-  const long long maxg = sc.W / (sc.u4 > sc.u8 ? sc.u4 : sc.u8);
+  // ... and a tile may spread over at most 31 CTAs (the owner finds them with one ballot)
+  long long minshare = sc.u4;  // u4 is the largest cost
+  const long long tile_cost[3] = {1ll * sc.S4 * sc.u4, 1ll * sc.S8 * sc.u8, 1ll * sc.S16 * sc.u16};
+  for (int f = 0; f < 3; ++f)
+    if ((tile_cost[f] + 29) / 30 > minshare) minshare = (tile_cost[f] + 29) / 30;
+  const long long maxg = sc.W / minshare;
   if (maxg < G) G = static_cast<int>(maxg);
   if (G < 1) G = 1;
   sc.G = G;
@@ -532,17 +576,31 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
   a.slot_bytes = (img_bytes(0, ck) + 127) & ~127;
   const int nt = h.M <= 8 ? 1 : 2;
   // shared memory: weight ring | flush ring | output metadata | activations (if they fit)
-  const int fixed = (kFlushRing / nt) * kMmaWarps * kTileRows * 8 * nt * 4 + kMetaSegs * kTileRows * 12;
+  // flush ring: slots of 12 warps x 16 rows x M partial sums, 24 KB at most, 2..8 deep
+  const int fl_slot = kMmaWarps * kTileRows * h.M * 4;
+  int fdepth = 24576 / fl_slot;
+  if (fdepth > kFlushRing) fdepth = kFlushRing;
+  if (fdepth < 2) fdepth = 2;
+  a.flush_depth = fdepth;
+  const int fixed = fdepth * fl_slot + kMetaSegs * kTileRows * 12;
   const int total_budget = 110 * 1024;  // two CTAs (this layer's and the next one's) share an SM
   int xbytes = h.M * (2 * h.K + 16);
   bool xs = true;
-  if (fixed + xbytes + 2 * a.slot_bytes > total_budget || xbytes > 44 * 1024) {
+  // The ring depth must be a multiple of the number of warp groups: then a slot is always
+  // consumed by the same group, whose waits on that slot's barrier follow each other phase
+  // by phase.  (With another depth a group could test a phase parity on a barrier it did not
+  // follow, see a stale "complete", read the slot early and arrive twice on its empty barrier.)
+  auto depth = [&](int xb) {
+    int n = (total_budget - fixed - xb) / a.slot_bytes;
+    if (n > kMaxStages) n = kMaxStages;
+    return (n / kGroups) * kGroups;
+  };
+  if (xbytes > 44 * 1024 || depth(xbytes) < kGroups) {
     xs = false;
     xbytes = 0;
   }
-  int nst = (total_budget - fixed - xbytes) / a.slot_bytes;
-  if (nst > kMaxStages) nst = kMaxStages;
-  if (nst < 2) nst = 2;
+  int nst = depth(xbytes);
+  if (nst < kGroups) nst = kGroups;  // 3 x 19 KB always fits beside the fixed part
   a.nstages = nst;
   const int smem = nst * a.slot_bytes + fixed + xbytes;
 
@@ -561,7 +619,11 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(G));
+#ifdef RDQ_TIMELINE
+  cfg.blockDim = dim3(kThreads + 32);  // + arrival monitor warp
+#else
   cfg.blockDim = dim3(kThreads);
+#endif
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];

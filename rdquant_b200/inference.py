@@ -137,6 +137,66 @@ class FusedMixedLinear(nn.Module):
                    marlin_data=None, fused_data=fd)
 
 
+class GraphedDecodeStep:
+    """One decode step over several packed linears as a single CUDA-graph replay.
+
+    The graph holds, for every layer, the copy of its activation rows from a pinned host
+    buffer to the device, the fused GEMV (programmatic dependent launch between layers) and
+    the copy of the result to a pinned host buffer.  ``run()`` replays it and waits for the
+    results, so a caller holding host-side activations pays one launch per step instead of
+    three calls per layer.  (The reference's end-to-end timings rely on CUDA-graph capture
+    of the decode step the same way, benchmarks/bench_e2e.py:103-155.)
+    """
+
+    def __init__(self, modules, m: int = 1, use_pdl: bool = True) -> None:
+        self.modules = list(modules)
+        dev = self.modules[0].inv_perm.device
+        # one pinned staging buffer each way: a single copy node per direction in the graph
+        ks = [m * mod.K for mod in self.modules]
+        ns = [m * mod.N for mod in self.modules]
+        self._x_all_host = torch.zeros(sum(ks), dtype=torch.float16).pin_memory()
+        self._y_all_host = torch.zeros(sum(ns), dtype=torch.float16).pin_memory()
+        self._x_all_dev = torch.zeros(sum(ks), dtype=torch.float16, device=dev)
+        self._y_all_dev = torch.zeros(sum(ns), dtype=torch.float16, device=dev)
+
+        def views(flat, sizes, cols):
+            out, off = [], 0
+            for sz, c in zip(sizes, cols):
+                out.append(flat[off:off + sz].view(m, c))
+                off += sz
+            return out
+
+        self.x_host = views(self._x_all_host, ks, [mod.K for mod in self.modules])
+        self.y_host = views(self._y_all_host, ns, [mod.N for mod in self.modules])
+        self._x_dev = views(self._x_all_dev, ks, [mod.K for mod in self.modules])
+        self._y_dev = views(self._y_all_dev, ns, [mod.N for mod in self.modules])
+        self._stream = torch.cuda.Stream(dev)
+        self._graph = torch.cuda.CUDAGraph()
+        cuda = get_rdquant_cuda()
+        flags = _lib.RDQ_GEMV_PDL if use_pdl else 0
+        biases = [mod.bias.detach().to(device=dev, dtype=torch.float16).contiguous() if mod.bias is not None else None
+                  for mod in self.modules]
+
+        def body():
+            self._x_all_dev.copy_(self._x_all_host, non_blocking=True)
+            for i, mod in enumerate(self.modules):
+                cuda.mixed_gemv(self._x_dev[i], mod._fd(), biases[i], flags, out=self._y_dev[i])
+            self._y_all_host.copy_(self._y_all_dev, non_blocking=True)
+
+        with torch.cuda.stream(self._stream):
+            body()  # first calls outside capture (library set-up, lazy module loading)
+            self._stream.synchronize()
+            with torch.cuda.graph(self._graph, stream=self._stream):
+                body()
+
+    def run(self):
+        """Replay: ``x_host`` -> device -> linears -> ``y_host``; returns ``y_host`` when complete."""
+        with torch.cuda.stream(self._stream):
+            self._graph.replay()
+        self._stream.synchronize()
+        return self.y_host
+
+
 # The grouped two-launch module of the reference (rdquant/inference.py:144-391) has the same
 # contract; one class serves both names.
 MarlinMixedLinear = FusedMixedLinear

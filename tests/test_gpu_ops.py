@@ -60,3 +60,20 @@ def test_fused_mixed_linear_module(layers):
         assert onp.rel_err(y.cpu().float().numpy(), y_ref) < TOL, m
     with pytest.raises(RuntimeError):
         mod(torch.randn(1, k).half())  # CPU input: no host path
+
+
+def test_graphed_decode_step(layers):
+    from rdquant_b200.inference import GraphedDecodeStep
+
+    mods = []
+    for name in ("mixed_384x256", "alloc_512x256"):
+        layer, splits, k = golden_layer_torch(layers[name])
+        mods.append(FusedMixedLinear.from_layer_data(layer, splits, k, "cuda"))
+    step = GraphedDecodeStep(mods, m=2)
+    for call in range(2):
+        xs = [torch.randn(2, mod.K).half() for mod in mods]
+        for xh, x in zip(step.x_host, xs):
+            xh.copy_(x)
+        ys = step.run()
+        for mod, x, y in zip(mods, xs, ys):
+            assert torch.equal(y, mod(x.cuda()).cpu()), call
