@@ -143,7 +143,9 @@ __device__ __forceinline__ void ttl_mark_(int slot, int ttl_m) {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   if (blockIdx.x < 148 && slot < 32) g_ttimeline[g_tl_base + blockIdx.x * 32 + slot] = t;
 }
-#define TTL_MARK(slot) do { if ((threadIdx.x & 31) == 0) ttl_mark_(slot, a.M); } while (0)
+// launches of the benchmark block are told apart by their shapes (debug build only)
+#define TTL_ID (a.K == 2560 ? (a.n4 + a.n8 + a.n16 > 10000 ? 3 : 1) : (a.K == 4096 ? 2 : 4))
+#define TTL_MARK(slot) do { if ((threadIdx.x & 31) == 0) ttl_mark_(slot, TTL_ID); } while (0)
 // fine-grained per-stage clocks of two CTAs of the M == 3 launch
 __device__ long long g_tstage[2 * 48 * 8];
 #define TST(idx_, col_) do { if (a.n4 + a.n8 + a.n16 > 15000 && (blockIdx.x == 10 || blockIdx.x == 100) && (idx_) < 48) \

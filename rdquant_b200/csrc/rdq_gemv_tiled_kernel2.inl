@@ -151,6 +151,22 @@ __device__ __forceinline__ void stage_fp16(float (&acc)[NT][2][4], uint32_t lm_a
   if (i < npairs) one(0);
 }
 
+// Stage list entry (one 32-bit word per image this CTA streams, in processing order):
+//   bits 1:0 format, bit 2 "flush after this stage", bits 12:3 chunk index inside the tile,
+//   bits 31:13 image index relative to the CTA's first image.
+constexpr uint32_t kEntFlush = 4u;
+
+// first image, image count and format of tile gtile
+__device__ __forceinline__ void tile_geom(const TSched &sc, int gtile, int &first_img, int &S, int &fmt) {
+  if (gtile < sc.t4) {
+    fmt = 0; S = sc.S4; first_img = gtile * sc.S4;
+  } else if (gtile < sc.t4 + sc.t8) {
+    fmt = 1; S = sc.S8; first_img = sc.e4 + (gtile - sc.t4) * sc.S8;
+  } else {
+    fmt = 2; S = sc.S16; first_img = sc.e8 + (gtile - sc.t4 - sc.t8) * sc.S16;
+  }
+}
+
 // NT = number of 8-row activation groups (1: M <= 8, 2: M <= 16)
 template <int NT, bool XS>
 __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledArgs a,
@@ -158,8 +174,8 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t bar_full[kMaxStages];
   __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
-  __shared__ __align__(8) uint64_t fl_full[kFlushRing];
-  __shared__ __align__(8) uint64_t fl_empty[kFlushRing];
+  __shared__ __align__(8) uint64_t fl_full[kGroups][kFlushRing];
+  __shared__ __align__(8) uint64_t fl_empty[kGroups][kFlushRing];
   __shared__ __align__(8) uint64_t bar_x;
 
   const int tid = threadIdx.x;
@@ -168,22 +184,26 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
   const int K = a.K, M = a.M;
   const int N = a.n4 + a.n8 + a.n16;
   const int nst = a.nstages;
-  // flush ring: fdepth slots of [12 warps][16 rows][mp activation rows] partial sums
-  const int mp = M, fdepth = a.flush_depth;
-  const int slot_floats = kMmaWarps * kTileRows * mp;
+  // flush rings, one per warp group: fdepth slots of [4 warps][16 rows][mp] partial sums
+  const int mp = (M + 3) & ~3, fdepth = a.flush_depth;  // rows of four floats: the epilogue reads 16 B at a time
+  const int gslot_floats = kWarpsPerGroup * kTileRows * mp;
   float *flush = reinterpret_cast<float *>(smem + nst * a.slot_bytes);
-  int *meta_col = reinterpret_cast<int *>(flush + fdepth * slot_floats);
+  int *meta_col = reinterpret_cast<int *>(flush + kGroups * fdepth * gslot_floats);
   float *meta_scl = reinterpret_cast<float *>(meta_col + kMetaSegs * kTileRows);
   float *meta_bia = meta_scl + kMetaSegs * kTileRows;
-  uint8_t *xsm = reinterpret_cast<uint8_t *>(meta_bia + kMetaSegs * kTileRows);
+  uint32_t *list = reinterpret_cast<uint32_t *>(meta_bia + kMetaSegs * kTileRows);
+  uint32_t *segtab = list + kMaxList;
+  float *vstage = reinterpret_cast<float *>(segtab + kMaxList);  // [16 rows][16] finished sums of one tile
+  uint8_t *xsm = reinterpret_cast<uint8_t *>(vstage + kTileRows * 16);
   const int xpitch = 2 * a.K + 16;  // activation row pitch in shared memory: skewed against bank conflicts
 
   // lane L holds the first image of CTA bx + L (one call site for the 64-bit divisions)
   const int bnd = sc.boundary(static_cast<int>(blockIdx.x) + lane);
   const int s_begin = __shfl_sync(0xffffffffu, bnd, 0);
   const int s_end = __shfl_sync(0xffffffffu, bnd, 1);
-  const int first_tile = (s_end > s_begin) ? sc.tile_of_image(s_begin) : 0;
-  const int nseg = (s_end > s_begin) ? (sc.tile_of_image(s_end - 1) - first_tile + 1) : 0;
+  const int nimg = s_end - s_begin;
+  const int first_tile = (nimg > 0) ? sc.tile_of_image(s_begin) : 0;
+  const int nseg = (nimg > 0) ? (sc.tile_of_image(s_end - 1) - first_tile + 1) : 0;
   int32_t *status = a.flags + a.status_idx;
   const int ck = sc.ck;
   const int pitch = (ck >> 1) + 16;
@@ -194,10 +214,11 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
       mbar_init(smem_u32(&bar_full[i]), 1);
       mbar_init(smem_u32(&bar_empty[i]), kWarpsPerGroup);
     }
-    for (int i = 0; i < fdepth; ++i) {
-      mbar_init(smem_u32(&fl_full[i]), kMmaWarps);
-      mbar_init(smem_u32(&fl_empty[i]), 1);
-    }
+    for (int g = 0; g < kGroups; ++g)
+      for (int i = 0; i < fdepth; ++i) {
+        mbar_init(smem_u32(&fl_full[g][i]), kWarpsPerGroup);
+        mbar_init(smem_u32(&fl_empty[g][i]), 1);
+      }
     mbar_init(smem_u32(&bar_x), 1);
     mbar_init_fence();
   }
@@ -205,11 +226,43 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
   // Let the next kernel in the stream become resident as early as possible; until this
   // grid completes it only fills its own shared-memory ring with weights.
   pdl_launch_dependents();
+  if (nimg > kMaxList) {  // the launcher refuses such shapes; never reached
+    if (tid == 0) atomicExch(status, 8);
+    return;
+  }
 
   const uint32_t smem_base = smem_u32(smem);
 
   if (warp == kMmaWarps) {
     // ==================================================================== producer
+    // The whole warp first writes the stage list: the CTA's images in processing order --
+    // the (possibly split) first tile, whose partial sums another CTA waits for, then the
+    // (possibly split) last tile, which this CTA finishes, then the whole tiles in between.
+    {
+      int f0, S0, fmt0;
+      tile_geom(sc, first_tile, f0, S0, fmt0);
+      const int n0 = min(s_end, f0 + S0) - s_begin;  // images of the first tile
+      int nl = 0;                                    // images of the last tile
+      if (nseg >= 2) {
+        int fl, Sl, fmtl;
+        tile_geom(sc, first_tile + nseg - 1, fl, Sl, fmtl);
+        nl = s_end - max(s_begin, fl);
+      }
+      auto rel_of = [&](int it) { return it < n0 ? it : (it < n0 + nl ? nimg - nl + (it - n0) : it - nl); };
+      for (int it = lane; it < nimg; it += 32) {
+        const int rel = rel_of(it);
+        const int gt = sc.tile_of_image(s_begin + rel);
+        int f, S, fmt;
+        tile_geom(sc, gt, f, S, fmt);
+        uint32_t e = static_cast<uint32_t>(fmt) | (static_cast<uint32_t>(s_begin + rel - f) << 3) |
+                     (static_cast<uint32_t>(rel) << 13);
+        // the group that takes this stage (it % kGroups) hands its sums over after its last
+        // stage of the tile
+        if (it + kGroups >= nimg || sc.tile_of_image(s_begin + rel_of(it + kGroups)) != gt) e |= kEntFlush;
+        list[it] = e;
+      }
+      __syncwarp();
+    }
     if (lane != 0) return;
     // The ring is filled with weights first (they do not depend on the preceding kernel);
     // only then wait for that kernel and fetch the activations it produced.
@@ -228,34 +281,33 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
         mbar_arrive(bx);
       }
     };
-    int it = 0, slot = 0, round = 0;
-    for (int q = 0; q < nseg; ++q) {
-      const TSeg sg = tseg_at(sc, s_begin, s_end, first_tile + tseg_order(q, nseg));
-      const uint32_t bytes = static_cast<uint32_t>(img_bytes(sg.fmt, ck));
-      for (int c = sg.c0; c < sg.c1; ++c, ++it) {
-        if (round > 0) {
-          send_x();
-          if (!mbar_wait(smem_u32(&bar_empty[slot]), (round - 1) & 1)) {
-            atomicExch(status, 1);
-            return;
-          }
+    int slot = 0, round = 0;
+#pragma unroll 1
+    for (int it = 0; it < nimg; ++it) {
+      const uint32_t e = list[it];
+      const uint32_t bytes = static_cast<uint32_t>((e & 3u) == 0 ? sc.img4 : sc.img8);
+      if (round > 0) {
+        send_x();
+        if (!mbar_wait(smem_u32(&bar_empty[slot]), (round - 1) & 1)) {
+          atomicExch(status, 1);
+          return;
         }
-        const uint32_t full = smem_u32(&bar_full[slot]);
-        TST(it, 0);
-        mbar_arrive_expect_tx(full, bytes);
-        bulk_g2s(smem_base + slot * a.slot_bytes, a.tiled + sc.image_offset(sg.first_img + c), bytes, full);
-        if (++slot == nst) { slot = 0; ++round; }
       }
+      const uint32_t full = smem_u32(&bar_full[slot]);
+      TST(it, 0);
+      mbar_arrive_expect_tx(full, bytes);
+      bulk_g2s(smem_base + slot * a.slot_bytes, a.tiled + sc.image_offset(s_begin + static_cast<int>(e >> 13)), bytes,
+               full);
+      if (++slot == nst) { slot = 0; ++round; }
     }
     send_x();
     return;
   }
 
-#ifdef RDQ_TIMELINE
+#ifdef RDQ_TL_MONITOR
   if (warp == kMmaWarps + 2) {
     // debug only: records when each stage's bytes have landed
     if (lane != 0) return;
-    int nimg = s_end - s_begin;
     for (int it = 0, slot = 0, round = 0; it < nimg; ++it) {
       bool ok = false;
       for (int spin = 0; spin < 4000000 && !ok; ++spin) ok = mbar_try(smem_u32(&bar_full[slot]), round & 1, 0u);
@@ -297,6 +349,69 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
         }
       }
     }
+    // Segment table: one word per tile segment, in processing order --
+    //   bits 8:0 tile index inside the CTA, bit 9 "tile starts here", bit 10 "tile ends here",
+    //   bits 13:11 warp groups that hold partial sums of it, bits 17:14 / 21:18 / 25:22 the
+    //   position (flush count modulo twice the ring depth) of each group's hand-over.
+    // Built by the whole warp with a prefix sum over the groups' flush counts.
+    {
+      int f0, S0, fmt0;
+      tile_geom(sc, first_tile, f0, S0, fmt0);
+      const int n0 = min(s_end, f0 + S0) - s_begin;  // images of the first tile
+      int nl = 0;                                    // images of the last tile
+      if (nseg >= 2) {
+        int fl, Sl, fmtl;
+        tile_geom(sc, first_tile + nseg - 1, fl, Sl, fmtl);
+        nl = s_end - max(s_begin, fl);
+      }
+      int carry = 0;  // flush counts so far: 10 bits per group
+      for (int base = 0; base < nseg; base += 32) {
+        const int q = base + lane;
+        int inc = 0;
+        uint32_t e = 0;
+        if (q < nseg) {
+          const int idx = tseg_order(q, nseg);
+          int f, S, fmt;
+          tile_geom(sc, first_tile + idx, f, S, fmt);
+          const int ia = max(s_begin, f), ib = min(s_end, f + S);
+          const int nstage = ib - ia;
+          const int it0 = (q == 0) ? 0 : (q == 1 ? n0 : n0 + nl + (f - (s_begin + n0)));
+          const int g0 = it0 % kGroups;
+          e = static_cast<uint32_t>(idx) | (ia == f ? 1u << 9 : 0u) | (ib == f + S ? 1u << 10 : 0u);
+#pragma unroll
+          for (int g = 0; g < kGroups; ++g) {
+            int d = g - g0;
+            if (d < 0) d += kGroups;
+            if (d < nstage) {
+              inc |= 1 << (10 * g);
+              e |= 1u << (11 + g);
+            }
+          }
+        }
+        int x = inc;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const int y = __shfl_up_sync(0xffffffffu, x, off);
+          if (lane >= off) x += y;
+        }
+        const int before = x - inc + carry;
+#pragma unroll
+        for (int g = 0; g < kGroups; ++g)
+          e |= static_cast<uint32_t>(((before >> (10 * g)) & 1023) % (2 * fdepth)) << (14 + 4 * g);
+        if (q < nseg) segtab[q] = e;
+        carry += __shfl_sync(0xffffffffu, x, 31);
+      }
+    }
+    // a split tile whose first image this CTA holds (only its last tile can be one): the
+    // other parts come from the CTAs bx + 1 .. b_last, in that order
+    int b_last = blockIdx.x;
+    {
+      int f, S, fmt;
+      tile_geom(sc, first_tile + nseg - 1, f, S, fmt);
+      const int s_last = f + S - 1;
+      b_last += __popc(__ballot_sync(0xffffffffu, lane >= 1 && bnd <= s_last && bnd < sc.e16));
+      if (lane == 0 && b_last >= static_cast<int>(blockIdx.x) + 31) atomicExch(status, 7);
+    }
     __syncwarp();
     TTL_MARK(1);
     // y, workspace and flags belong to this launch only once the preceding grid is done
@@ -305,20 +420,31 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
       return;
     }
     TTL_MARK(2);
-    // lane = (row, half): each half sums six of the twelve partials of its row
+    // work item = (row, quad of four activation rows): lane L takes item L, and item L + 32
+    // when M > 8
     const int row = lane & 15;
-    const int half = lane >> 4;
-    int fslot = 0, fround = 0;
+    const int nitem = (M > 8) ? 2 : 1;
+    float *ws_row = a.workspace + 1ll * blockIdx.x * 256 + row * 16;
 #pragma unroll 1
     for (int q = 0; q < nseg; ++q) {
-      const int idx = tseg_order(q, nseg);
-      const TSeg sg = tseg_at(sc, s_begin, s_end, first_tile + idx);
-      if (!mbar_wait(smem_u32(&fl_full[fslot]), fround & 1)) {
-        if (lane == 0) atomicExch(status, 2);
-        return;
+      const uint32_t e = segtab[q];
+      const int idx = e & 511;
+      const bool starts = (e >> 9) & 1, ends = (e >> 10) & 1;
+      // ring slot of group g's hand-over for this segment (position below the ring depth:
+      // even round, else odd round)
+      auto gslot = [&](int g) {
+        const int code = (e >> (14 + 4 * g)) & 15;
+        return code >= fdepth ? code - fdepth : code;
+      };
+#pragma unroll
+      for (int g = 0; g < kGroups; ++g) {
+        const int par = ((e >> (14 + 4 * g)) & 15) >= fdepth;
+        if (((e >> (11 + g)) & 1) && !mbar_wait(smem_u32(&fl_full[g][gslot(g)]), par)) {
+          if (lane == 0) atomicExch(status, 2);
+          return;
+        }
       }
       if (lane == 0) TST(q, 5);
-      const float *buf = flush + fslot * slot_floats + (half * (kMmaWarps / 2) * kTileRows + row) * mp;
       int col;
       float scl, bia;
       if (idx < kMetaSegs) {
@@ -326,36 +452,54 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
         scl = meta_scl[idx * kTileRows + row];
         bia = meta_bia[idx * kTileRows + row];
       } else {
-        const int prow = sg.gtile * kTileRows + row;
+        const int gt = first_tile + idx;
+        const int prow = gt * kTileRows + row;
         col = a.perm ? a.perm[prow] : prow;
-        scl = (sg.fmt == 1) ? a.s8[prow - a.n4] : (sg.fmt == 0 ? a.global4 : 1.f);
+        scl = (gt < sc.t4) ? a.global4 : (gt < sc.t4 + sc.t8 ? a.s8[prow - a.n4] : 1.f);
         bia = a.bias ? __half2float(a.bias[col]) : 0.f;
       }
-      // split tile whose first image this CTA holds: the other parts come from the CTAs
-      // bx + 1 .. b_last, in that order
-      int b_last = blockIdx.x;
-      if (sg.starts && !sg.ends) {
-        const int s_last = sg.first_img + sg.S - 1;
-        b_last += __popc(__ballot_sync(0xffffffffu, lane >= 1 && bnd <= s_last && bnd < sc.e16));
-        if (lane == 0 && b_last >= static_cast<int>(blockIdx.x) + 31) atomicExch(status, 7);
-      }
-      float *ws = a.workspace + 1ll * blockIdx.x * 256 + row * 16;
-      bool ok = true;
+      // Sum first and give the flush slots back at once: the barrier arrival is a release,
+      // and behind a global store it would wait for that store to be acknowledged.
 #pragma unroll 1
-      for (int m = 0; m < M; ++m) {
-        float v = 0.f;
+      for (int j = 0; j < nitem; ++j) {
+        const int m0 = ((lane >> 4) + 2 * j) * 4;
+        if (m0 < M) {
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int w = 0; w < kMmaWarps / 2; ++w) v += buf[w * kTileRows * mp + m];
-        v += __shfl_xor_sync(0xffffffffu, v, 16);
-        if (half) continue;
-        if (!sg.starts) {
+          for (int g = 0; g < kGroups; ++g) {
+            if ((e >> (11 + g)) & 1) {
+#pragma unroll
+              for (int w = 0; w < kWarpsPerGroup; ++w) {
+                const float4 p = *reinterpret_cast<const float4 *>(
+                    flush + (g * fdepth + gslot(g)) * gslot_floats + (w * kTileRows + row) * mp + m0);
+                v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+              }
+            }
+          }
+          *reinterpret_cast<float4 *>(vstage + row * 16 + m0) = v;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
+#pragma unroll
+        for (int g = 0; g < kGroups; ++g)
+          if ((e >> (11 + g)) & 1) mbar_arrive(smem_u32(&fl_empty[g][gslot(g)]));
+      }
+      if (lane == 0) TST(q, 4);
+      const int b_hi = (starts && !ends) ? b_last : static_cast<int>(blockIdx.x);
+      bool ok = true;
+      __syncwarp();
+#pragma unroll 1
+      for (int m = lane >> 4; m < M; m += 2) {
+        float v = vstage[row * 16 + m];
+        if (!starts) {
           // continuation of a tile another CTA started: store the partial sums into this
           // CTA's workspace slot (idle words read 0xffffffff); the owner polls them
-          ws[m] = v;
+          ws_row[m] = v;
           continue;
         }
 #pragma unroll 1
-        for (int b = blockIdx.x + 1; b <= b_last; ++b) {
+        for (int b = blockIdx.x + 1; b <= b_hi; ++b) {
           float *pw = a.workspace + 1ll * b * 256 + row * 16 + m;
           uint32_t bits = 0xffffffffu;
 #pragma unroll 1
@@ -369,9 +513,7 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
         }
         a.y[1ll * m * N + col] = __float2half_rn(fmaf(v, scl, bia));
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&fl_empty[fslot]));
-      if (++fslot == fdepth) { fslot = 0; ++fround; }
+      __syncwarp();  // vstage is rewritten for the next tile
       if (__any_sync(0xffffffffu, !ok)) {
         if (lane == 0) atomicExch(status, 3);
         return;
@@ -404,6 +546,7 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
 
   // x is produced by the preceding kernel: do not touch it before the producer thread has
   // seen that kernel complete (and, with XS, has copied the rows into shared memory).
+  // The stage list is complete by then, too.
   if (!mbar_wait(smem_u32(&bar_x), 0)) {
     if (lane == 0) atomicExch(status, 6);
     return;
@@ -417,95 +560,65 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
     xb[n] = XS ? static_cast<uint64_t>(smem_u32(xsm) + (m < M ? m : 0) * xpitch)
                : reinterpret_cast<uint64_t>(a.x + 1ll * (m < M ? m : 0) * K);
   }
-
-#ifdef RDQ_TIMELINE
-  long long cyc_wait = 0, cyc_comp = 0, cyc_flush = 0, cyc_o2 = 0, cyc_flwait = 0, cyc_flwrite = 0, tprev = clock64();
   if (warp == 0) TTL_MARK(15);
-  if (warp == 0 && lane == 0) TST(47, 7);
-#define TTL_LAP(acc_) do { const long long tnow_ = clock64(); acc_ += tnow_ - tprev; tprev = tnow_; } while (0)
-#else
-#define TTL_LAP(acc_) do { } while (0)
-#endif
-  int it = 0, slot = 0, round = 0, fslot = 0, fround = 0;
-#pragma unroll 1
-  for (int q = 0; q < nseg; ++q) {
-    const TSeg sg = tseg_at(sc, s_begin, s_end, first_tile + tseg_order(q, nseg));
-#pragma unroll 1
-    for (int c = sg.c0; c < sg.c1; ++c, ++it) {
-      // stages go round robin to the warp groups: a warp then has a whole quarter of a stage
-      // to work on per barrier wait
-      if (it % kGroups != grp) {
-        if (++slot == nst) { slot = 0; ++round; }
-        continue;
-      }
-      TTL_LAP(cyc_flush);
-      if (!mbar_wait(smem_u32(&bar_full[slot]), round & 1)) {
-        if (lane == 0) atomicExch(status, 4);
-        return;
-      }
-      TTL_LAP(cyc_wait);
-      if (wq == 0 && lane == 0) TST(it, 1);
-      const uint32_t sbase = smem_base + slot * a.slot_bytes;
-      // inside a group the warps take turns on the pair ranges, so uneven splits average out
-      const int lw = (wq + it / kGroups) & (kWarpsPerGroup - 1);
-      if (sg.fmt == 0) {
-        const int lo = lw * npair / kWarpsPerGroup, hi = (lw + 1) * npair / kWarpsPerGroup;
-        stage_fp4<NT, XS>(acc, sbase + lm_lane + lo * 32, sbase + sc_lane + lo * 4, sbase + sc_lane + 8 * spitch + lo * 4,
-                          xb, 2 * (c * ck + lo * 64 + t * 8), hi - lo, sel);
-      } else if (sg.fmt == 1) {
-        const int lo = lw * npair / kWarpsPerGroup, hi = (lw + 1) * npair / kWarpsPerGroup;
-        stage_fp8<NT, XS>(acc, sbase + lm_lane + lo * 32, xb, 2 * (c * (ck >> 1) + lo * 32 + t * 4), hi - lo);
-      } else {
-        const int lo = lw * npair / kWarpsPerGroup, hi = (lw + 1) * npair / kWarpsPerGroup;
-        stage_fp16<NT, XS>(acc, sbase + lm_lane + lo * 32, xb, 2 * (c * (ck >> 2) + lo * 16 + t * 2), hi - lo);
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_empty[slot]));
-      if (++slot == nst) { slot = 0; ++round; }
-      TTL_LAP(cyc_comp);
-      if (wq == 0 && lane == 0) TST(it, 2);
-    }
-    if (warp == 0 && q == 0) TTL_MARK(4);
+  if (warp == 0 && lane == 0) TST(47, 6);
 
-    // ---- hand the partial sums of this segment to the epilogue warp
-    TTL_LAP(cyc_o2);
-    if (lane == 0 && warp == 0) TST(q, 3);
-    if (fround > 0 && !mbar_wait(smem_u32(&fl_empty[fslot]), (fround - 1) & 1)) {
-      if (lane == 0) atomicExch(status, 5);
+  // Stage it goes to warp group it % kGroups; the ring depth is a multiple of kGroups, so a
+  // group meets the same slots again and again and follows their barriers phase by phase.
+  float *fl_base = flush + grp * fdepth * gslot_floats + wq * kTileRows * mp;
+  int slot = grp, round = 0, fslot = 0, fround = 0;
+  int turn = 0;  // stages this group has taken: rotates the pair ranges among its warps
+#pragma unroll 1
+  for (int it = grp; it < nimg; it += kGroups, ++turn) {
+    const uint32_t e = list[it];
+    if (!mbar_wait(smem_u32(&bar_full[slot]), round & 1)) {
+      if (lane == 0) atomicExch(status, 4);
       return;
     }
-    TTL_LAP(cyc_flwait);
-    float *buf = flush + fslot * slot_floats + warp * kTileRows * mp;
-#pragma unroll
-    for (int n = 0; n < NT; ++n) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int r = g + (i >> 1) * 8;
-        const int m = n * 8 + 2 * t + (i & 1);
-        if (m < M) buf[r * mp + m] = acc[n][0][i] + acc[n][1][i];
-        acc[n][0][i] = 0.f;
-        acc[n][1][i] = 0.f;
-      }
+    if (wq == 0 && lane == 0) TST(it, 1);
+    const uint32_t sbase = smem_base + slot * a.slot_bytes;
+    const int c = (e >> 3) & 1023;
+    const int fmt = e & 3;
+    // inside a group the warps take turns on the pair ranges, so uneven splits average out
+    const int lw = (wq + turn) & (kWarpsPerGroup - 1);
+    const int lo = lw * npair / kWarpsPerGroup, hi = (lw + 1) * npair / kWarpsPerGroup;
+    if (fmt == 0) {
+      stage_fp4<NT, XS>(acc, sbase + lm_lane + lo * 32, sbase + sc_lane + lo * 4, sbase + sc_lane + 8 * spitch + lo * 4,
+                        xb, 2 * (c * ck + lo * 64 + t * 8), hi - lo, sel);
+    } else if (fmt == 1) {
+      stage_fp8<NT, XS>(acc, sbase + lm_lane + lo * 32, xb, 2 * (c * (ck >> 1) + lo * 32 + t * 4), hi - lo);
+    } else {
+      stage_fp16<NT, XS>(acc, sbase + lm_lane + lo * 32, xb, 2 * (c * (ck >> 2) + lo * 16 + t * 2), hi - lo);
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(smem_u32(&fl_full[fslot]));
-    if (++fslot == fdepth) { fslot = 0; ++fround; }
-    TTL_LAP(cyc_flwrite);
-    if (lane == 0 && warp == 0) TST(q, 4);
+    if (lane == 0) mbar_arrive(smem_u32(&bar_empty[slot]));
+    if (wq == 0 && lane == 0) TST(it, 2);
+    slot += kGroups;
+    if (slot >= nst) { slot -= nst; ++round; }
+
+    if (e & kEntFlush) {
+      // ---- the group's last stage of this tile: hand the partial sums to the epilogue warp
+      if (fround > 0 && !mbar_wait(smem_u32(&fl_empty[grp][fslot]), (fround - 1) & 1)) {
+        if (lane == 0) atomicExch(status, 5);
+        return;
+      }
+      float *buf = fl_base + fslot * gslot_floats;
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = g + (i >> 1) * 8;
+          const int m = n * 8 + 2 * t + (i & 1);
+          if (m < M) buf[r * mp + m] = acc[n][0][i] + acc[n][1][i];
+          acc[n][0][i] = 0.f;
+          acc[n][1][i] = 0.f;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&fl_full[grp][fslot]));
+      if (++fslot == fdepth) { fslot = 0; ++fround; }
+    }
   }
-#ifdef RDQ_TIMELINE
-  if (warp == 5 && lane == 0 && blockIdx.x < 148) {
-    const int ttl_m = a.M;
-    g_ttimeline[g_tl_base + blockIdx.x * 32 + 16] = cyc_wait;
-    g_ttimeline[g_tl_base + blockIdx.x * 32 + 17] = cyc_comp;
-    g_ttimeline[g_tl_base + blockIdx.x * 32 + 18] = cyc_flush;
-    g_ttimeline[g_tl_base + blockIdx.x * 32 + 19] = it;
-    g_ttimeline[g_tl_base + blockIdx.x * 32 + 12] = cyc_flwait;
-    g_ttimeline[g_tl_base + blockIdx.x * 32 + 13] = cyc_flwrite;
-    g_ttimeline[g_tl_base + blockIdx.x * 32 + 14] = nseg;
-    g_ttimeline[g_tl_base + blockIdx.x * 32 + 11] = cyc_o2;
-  }
-#endif
 }
 
 }  // namespace
@@ -544,12 +657,6 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
   sc.u4 = 10;
   sc.u8 = 6;
   sc.u16 = 5;
-  if (const char *env = getenv("RDQ_TILED_COST")) {  // A/B knob: "u4,u8,u16"
-    int c4 = 0, c8 = 0, c16 = 0;
-    if (sscanf(env, "%d,%d,%d", &c4, &c8, &c16) == 3 && c4 >= c8 && c8 >= c16 && c16 >= 1 && c4 <= 4096) {
-      sc.u4 = c4; sc.u8 = c8; sc.u16 = c16;
-    }
-  }
   sc.img4 = img_bytes(0, ck);
   sc.img8 = img_bytes(1, ck);
   sc.w4 = 1ll * sc.e4 * sc.u4;
@@ -567,6 +674,8 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
   if (maxg < G) G = static_cast<int>(maxg);
   if (G < 1) G = 1;
   sc.G = G;
+  RDQ_REQUIRE(sc.W / G / sc.u16 + 2 <= kMaxList, RDQ_E_UNSUPPORTED,
+              "layer too large for the tiled GEMV: more than %d images per CTA", kMaxList);
 
   TiledArgs a;
   a.x = h.x; a.M = h.M; a.tiled = h.tiled; a.s8 = h.s8; a.global4 = h.global4; a.perm = h.perm;
@@ -576,13 +685,13 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
   a.slot_bytes = (img_bytes(0, ck) + 127) & ~127;
   const int nt = h.M <= 8 ? 1 : 2;
   // shared memory: weight ring | flush ring | output metadata | activations (if they fit)
-  // flush ring: slots of 12 warps x 16 rows x M partial sums, 24 KB at most, 2..8 deep
-  const int fl_slot = kMmaWarps * kTileRows * h.M * 4;
-  int fdepth = 24576 / fl_slot;
+  // flush rings: slots of 12 warps x 16 rows x (M rounded up to 4) partial sums, 2..8 deep
+  const int fl_slot = kMmaWarps * kTileRows * ((h.M + 3) & ~3) * 4;
+  int fdepth = 12288 / fl_slot;
   if (fdepth > kFlushRing) fdepth = kFlushRing;
   if (fdepth < 2) fdepth = 2;
   a.flush_depth = fdepth;
-  const int fixed = fdepth * fl_slot + kMetaSegs * kTileRows * 12;
+  const int fixed = fdepth * fl_slot + kMetaSegs * kTileRows * 12 + kMaxList * 8 + kTileRows * 16 * 4;
   const int total_budget = 110 * 1024;  // two CTAs (this layer's and the next one's) share an SM
   int xbytes = h.M * (2 * h.K + 16);
   bool xs = true;
@@ -595,7 +704,8 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
     if (n > kMaxStages) n = kMaxStages;
     return (n / kGroups) * kGroups;
   };
-  if (xbytes > 44 * 1024 || depth(xbytes) < kGroups) {
+  // activations go to shared memory only while that leaves every warp group two ring slots
+  if (xbytes > 44 * 1024 || depth(xbytes) < min(2 * kGroups, depth(0))) {
     xs = false;
     xbytes = 0;
   }
@@ -619,7 +729,7 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(G));
-#ifdef RDQ_TIMELINE
+#ifdef RDQ_TL_MONITOR
   cfg.blockDim = dim3(kThreads + 32);  // + arrival monitor warp
 #else
   cfg.blockDim = dim3(kThreads);
