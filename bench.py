@@ -305,6 +305,11 @@ def main() -> None:
     for i in range(warmup):
         one_step(i)
     torch.cuda.synchronize()
+    # a kernel whose bounded waits ran out leaves a status word behind: stop here rather than
+    # time steps that each sit through their wait limits
+    bad = sum(int(fd["tile_counters"].abs().sum().item()) for l in layers for fd in l["fds"] if "tile_counters" in fd)
+    if bad:
+        raise RuntimeError(f"GEMV kernels reported {bad} non-zero status words during warm-up")
     stream = torch.cuda.Stream(device)
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(stream):

@@ -58,8 +58,11 @@ constexpr int kMmaWarps = 12;
 constexpr int kGroups = 3;          // warp groups; stage i is consumed by group i % 3
 constexpr int kWarpsPerGroup = 4;   // power of two
 static_assert(kGroups * kWarpsPerGroup == kMmaWarps, "warp groups must cover the MMA warps");
-constexpr int kThreads = (kMmaWarps + 2) * 32;  // + producer warp + epilogue warp
-constexpr int kFlushRing = 8;  // deepest flush ring
+constexpr int kEpiWarps = 3;
+constexpr int kThreads = (kMmaWarps + 1 + kEpiWarps) * 32;  // + producer warp + epilogue warps = 4 warpgroups
+// 512 threads: the launch bounds ask for two CTAs (this layer's and the next one's) per SM,
+// i.e. 64 registers per thread
+constexpr int kFlushRing = 2;  // slots of a hand-over ring (one per warp group and epilogue warp)
 constexpr int kMetaSegs = 32;
 constexpr int kMaxStages = 12;
 constexpr int kMaxList = 512;       // images one CTA can stream (stage list entries)

@@ -131,7 +131,7 @@ struct TiledArgs {
   int status_idx;
   int nstages;
   int slot_bytes;
-  int flush_depth;
+  int nepi;  // epilogue warps in use
 };
 
 #ifdef RDQ_TIMELINE

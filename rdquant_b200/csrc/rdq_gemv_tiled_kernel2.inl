@@ -3,6 +3,12 @@ namespace rdq {
 
 namespace {
 
+// scheduling cost of one NVFP4 / FP8 / FP16 image (build-time tunables)
+#ifndef RDQ_COST_U4
+#define RDQ_COST_U4 10
+#define RDQ_COST_U8 7
+#define RDQ_COST_U16 6
+#endif
 #ifndef RDQ_STAGE_UNROLL
 #define RDQ_STAGE_UNROLL 2
 #endif
@@ -152,8 +158,9 @@ __device__ __forceinline__ void stage_fp16(float (&acc)[NT][2][4], uint32_t lm_a
 }
 
 // Stage list entry (one 32-bit word per image this CTA streams, in processing order):
-//   bits 1:0 format, bit 2 "flush after this stage", bits 12:3 chunk index inside the tile,
-//   bits 31:13 image index relative to the CTA's first image.
+//   bits 1:0 format, bit 2 "hand over after this stage", bits 10:3 chunk index inside the
+//   tile, bits 12:11 the epilogue warp that finishes the tile, bits 31:13 image index relative
+//   to the CTA's first image.
 constexpr uint32_t kEntFlush = 4u;
 
 // first image, image count and format of tile gtile
@@ -169,13 +176,13 @@ __device__ __forceinline__ void tile_geom(const TSched &sc, int gtile, int &firs
 
 // NT = number of 8-row activation groups (1: M <= 8, 2: M <= 16)
 template <int NT, bool XS>
-__global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledArgs a,
+__global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_constant__ TiledArgs a,
                                                   const __grid_constant__ TSched sc) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t bar_full[kMaxStages];
   __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
-  __shared__ __align__(8) uint64_t fl_full[kGroups][kFlushRing];
-  __shared__ __align__(8) uint64_t fl_empty[kGroups][kFlushRing];
+  __shared__ __align__(8) uint64_t fl_full[kGroups][kEpiWarps][kFlushRing];
+  __shared__ __align__(8) uint64_t fl_empty[kGroups][kEpiWarps][kFlushRing];
   __shared__ __align__(8) uint64_t bar_x;
 
   const int tid = threadIdx.x;
@@ -184,17 +191,20 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
   const int K = a.K, M = a.M;
   const int N = a.n4 + a.n8 + a.n16;
   const int nst = a.nstages;
-  // flush rings, one per warp group: fdepth slots of [4 warps][16 rows][mp] partial sums
-  const int mp = (M + 3) & ~3, fdepth = a.flush_depth;  // rows of four floats: the epilogue reads 16 B at a time
+  // hand-over rings, one per (warp group, epilogue warp): kFlushRing slots of
+  // [4 warps][16 rows][mp] partial sums; each ring has one writer group and one reader warp,
+  // which both follow its barriers phase by phase
+  const int mp = (M + 3) & ~3;  // rows of four floats: the epilogue reads 16 B at a time
+  const int nepi = a.nepi;      // epilogue warps in use (1..kEpiWarps)
   const int gslot_floats = kWarpsPerGroup * kTileRows * mp;
   float *flush = reinterpret_cast<float *>(smem + nst * a.slot_bytes);
-  int *meta_col = reinterpret_cast<int *>(flush + kGroups * fdepth * gslot_floats);
+  int *meta_col = reinterpret_cast<int *>(flush + kGroups * nepi * kFlushRing * gslot_floats);
   float *meta_scl = reinterpret_cast<float *>(meta_col + kMetaSegs * kTileRows);
   float *meta_bia = meta_scl + kMetaSegs * kTileRows;
   uint32_t *list = reinterpret_cast<uint32_t *>(meta_bia + kMetaSegs * kTileRows);
   uint32_t *segtab = list + kMaxList;
-  float *vstage = reinterpret_cast<float *>(segtab + kMaxList);  // [16 rows][16] finished sums of one tile
-  uint8_t *xsm = reinterpret_cast<uint8_t *>(vstage + kTileRows * 16);
+  float *vstage = reinterpret_cast<float *>(segtab + kMaxList);  // per epilogue warp: [16 rows][16] finished sums of a tile
+  uint8_t *xsm = reinterpret_cast<uint8_t *>(vstage + kEpiWarps * kTileRows * 16);
   const int xpitch = 2 * a.K + 16;  // activation row pitch in shared memory: skewed against bank conflicts
 
   // lane L holds the first image of CTA bx + L (one call site for the 64-bit divisions)
@@ -215,10 +225,11 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
       mbar_init(smem_u32(&bar_empty[i]), kWarpsPerGroup);
     }
     for (int g = 0; g < kGroups; ++g)
-      for (int i = 0; i < fdepth; ++i) {
-        mbar_init(smem_u32(&fl_full[g][i]), kWarpsPerGroup);
-        mbar_init(smem_u32(&fl_empty[g][i]), 1);
-      }
+      for (int j = 0; j < kEpiWarps; ++j)
+        for (int i = 0; i < kFlushRing; ++i) {
+          mbar_init(smem_u32(&fl_full[g][j][i]), kWarpsPerGroup);
+          mbar_init(smem_u32(&fl_empty[g][j][i]), 1);
+        }
     mbar_init(smem_u32(&bar_x), 1);
     mbar_init_fence();
   }
@@ -254,8 +265,11 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
         const int gt = sc.tile_of_image(s_begin + rel);
         int f, S, fmt;
         tile_geom(sc, gt, f, S, fmt);
+        // position of the tile in processing order, and the epilogue warp that takes it
+        const int idx = gt - first_tile;
+        const int q = (idx == 0) ? 0 : (idx == nseg - 1 ? 1 : idx + 1);
         uint32_t e = static_cast<uint32_t>(fmt) | (static_cast<uint32_t>(s_begin + rel - f) << 3) |
-                     (static_cast<uint32_t>(rel) << 13);
+                     (static_cast<uint32_t>(q % nepi) << 11) | (static_cast<uint32_t>(rel) << 13);
         // the group that takes this stage (it % kGroups) hands its sums over after its last
         // stage of the tile
         if (it + kGroups >= nimg || sc.tile_of_image(s_begin + rel_of(it + kGroups)) != gt) e |= kEntFlush;
@@ -304,26 +318,20 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
     return;
   }
 
-#ifdef RDQ_TL_MONITOR
-  if (warp == kMmaWarps + 2) {
-    // debug only: records when each stage's bytes have landed
-    if (lane != 0) return;
-    for (int it = 0, slot = 0, round = 0; it < nimg; ++it) {
-      bool ok = false;
-      for (int spin = 0; spin < 4000000 && !ok; ++spin) ok = mbar_try(smem_u32(&bar_full[slot]), round & 1, 0u);
-      TST(it, 7);
-      if (++slot == nst) { slot = 0; ++round; }
-    }
-    return;
-  }
-#endif
-  if (warp == kMmaWarps + 1) {
-    // ================================================================ epilogue warp
+  if (warp > kMmaWarps) {
+    // =============================================================== epilogue warps
+    // The first nepi of them take the tile segments in turn: segment q (in processing
+    // order) belongs to warp q % nepi.
+    const int ej = warp - kMmaWarps - 1;
+    if (ej >= nepi) return;
+    float *vst = vstage + ej * kTileRows * 16;
     // output column, scale and bias of every row this CTA finishes: constants of the
-    // layer, fetched up front so that finishing a tile needs no global round trip
-    {
+    // layer, fetched up front so that finishing a tile needs no global round trip.  With
+    // more than one epilogue warp the first builds the segment table and the others do this.
+    if (ej > 0 || nepi == 1) {
       const int nmeta = min(nseg, kMetaSegs) * kTileRows;
-      for (int base = 0; base < nmeta; base += 128) {
+      const int nload = (nepi == 1) ? 1 : nepi - 1;
+      for (int base = (nepi == 1 ? 0 : ej - 1) * 128; base < nmeta; base += 128 * nload) {
         int col[4];
         float scl[4];
 #pragma unroll
@@ -351,10 +359,11 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
     }
     // Segment table: one word per tile segment, in processing order --
     //   bits 8:0 tile index inside the CTA, bit 9 "tile starts here", bit 10 "tile ends here",
-    //   bits 13:11 warp groups that hold partial sums of it, bits 17:14 / 21:18 / 25:22 the
-    //   position (flush count modulo twice the ring depth) of each group's hand-over.
-    // Built by the whole warp with a prefix sum over the groups' flush counts.
-    {
+    //   bits 13:11 warp groups that hold partial sums of it, bits 15:14 / 17:16 / 19:18 for
+    //   each group the number (modulo 4) of hand-overs it made to this segment's epilogue
+    //   warp before: ring slot = bit 0, barrier parity = bit 1.
+    // Built by one whole warp: a prefix sum over lanes q, q - nepi, q - 2 nepi, ...
+    if (ej == 0) {
       int f0, S0, fmt0;
       tile_geom(sc, first_tile, f0, S0, fmt0);
       const int n0 = min(s_end, f0 + S0) - s_begin;  // images of the first tile
@@ -364,9 +373,12 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
         tile_geom(sc, first_tile + nseg - 1, fl, Sl, fmtl);
         nl = s_end - max(s_begin, fl);
       }
-      int carry = 0;  // flush counts so far: 10 bits per group
+      int carry[kEpiWarps];  // hand-over counts so far per epilogue warp: 10 bits per group
+#pragma unroll
+      for (int j = 0; j < kEpiWarps; ++j) carry[j] = 0;
       for (int base = 0; base < nseg; base += 32) {
         const int q = base + lane;
+        const int qe = q % nepi;
         int inc = 0;
         uint32_t e = 0;
         if (q < nseg) {
@@ -389,17 +401,26 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
           }
         }
         int x = inc;
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
+        for (int off = nepi; off < 32; off <<= 1) {
           const int y = __shfl_up_sync(0xffffffffu, x, off);
           if (lane >= off) x += y;
         }
-        const int before = x - inc + carry;
+        int mycarry = carry[0];
 #pragma unroll
-        for (int g = 0; g < kGroups; ++g)
-          e |= static_cast<uint32_t>(((before >> (10 * g)) & 1023) % (2 * fdepth)) << (14 + 4 * g);
+        for (int j = 1; j < kEpiWarps; ++j)
+          if (qe == j) mycarry = carry[j];
+        const int before = x - inc + mycarry;
+#pragma unroll
+        for (int g = 0; g < kGroups; ++g) e |= static_cast<uint32_t>((before >> (10 * g)) & 3) << (14 + 2 * g);
         if (q < nseg) segtab[q] = e;
-        carry += __shfl_sync(0xffffffffu, x, 31);
+        // totals of this chunk per epilogue warp: held by the last lane of each residue class
+#pragma unroll
+        for (int j = 0; j < kEpiWarps; ++j) {
+          if (j < nepi) {
+            int last = 31 - (((base + 31) % nepi) - j + nepi) % nepi;
+            carry[j] += __shfl_sync(0xffffffffu, x, last);
+          }
+        }
       }
     }
     // a split tile whose first image this CTA holds (only its last tile can be one): the
@@ -412,7 +433,8 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
       b_last += __popc(__ballot_sync(0xffffffffu, lane >= 1 && bnd <= s_last && bnd < sc.e16));
       if (lane == 0 && b_last >= static_cast<int>(blockIdx.x) + 31) atomicExch(status, 7);
     }
-    __syncwarp();
+    // metadata and segment table are complete for all epilogue warps in use
+    asm volatile("bar.sync 1, %0;" ::"r"(nepi * 32) : "memory");
     TTL_MARK(1);
     // y, workspace and flags belong to this launch only once the preceding grid is done
     if (!mbar_wait(smem_u32(&bar_x), 0)) {
@@ -426,20 +448,14 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
     const int nitem = (M > 8) ? 2 : 1;
     float *ws_row = a.workspace + 1ll * blockIdx.x * 256 + row * 16;
 #pragma unroll 1
-    for (int q = 0; q < nseg; ++q) {
+    for (int q = ej; q < nseg; q += nepi) {
       const uint32_t e = segtab[q];
       const int idx = e & 511;
       const bool starts = (e >> 9) & 1, ends = (e >> 10) & 1;
-      // ring slot of group g's hand-over for this segment (position below the ring depth:
-      // even round, else odd round)
-      auto gslot = [&](int g) {
-        const int code = (e >> (14 + 4 * g)) & 15;
-        return code >= fdepth ? code - fdepth : code;
-      };
 #pragma unroll
       for (int g = 0; g < kGroups; ++g) {
-        const int par = ((e >> (14 + 4 * g)) & 15) >= fdepth;
-        if (((e >> (11 + g)) & 1) && !mbar_wait(smem_u32(&fl_full[g][gslot(g)]), par)) {
+        const int code = (e >> (14 + 2 * g)) & 3;
+        if (((e >> (11 + g)) & 1) && !mbar_wait(smem_u32(&fl_full[g][ej][code & 1]), code >> 1)) {
           if (lane == 0) atomicExch(status, 2);
           return;
         }
@@ -458,7 +474,7 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
         scl = (gt < sc.t4) ? a.global4 : (gt < sc.t4 + sc.t8 ? a.s8[prow - a.n4] : 1.f);
         bia = a.bias ? __half2float(a.bias[col]) : 0.f;
       }
-      // Sum first and give the flush slots back at once: the barrier arrival is a release,
+      // Sum first and give the ring slots back at once: the barrier arrival is a release,
       // and behind a global store it would wait for that store to be acknowledged.
 #pragma unroll 1
       for (int j = 0; j < nitem; ++j) {
@@ -468,30 +484,29 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
 #pragma unroll
           for (int g = 0; g < kGroups; ++g) {
             if ((e >> (11 + g)) & 1) {
+              const float *ring = flush + ((g * nepi + ej) * kFlushRing + ((e >> (14 + 2 * g)) & 1)) * gslot_floats;
 #pragma unroll
               for (int w = 0; w < kWarpsPerGroup; ++w) {
-                const float4 p = *reinterpret_cast<const float4 *>(
-                    flush + (g * fdepth + gslot(g)) * gslot_floats + (w * kTileRows + row) * mp + m0);
+                const float4 p = *reinterpret_cast<const float4 *>(ring + (w * kTileRows + row) * mp + m0);
                 v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
               }
             }
           }
-          *reinterpret_cast<float4 *>(vstage + row * 16 + m0) = v;
+          *reinterpret_cast<float4 *>(vst + row * 16 + m0) = v;
         }
       }
       __syncwarp();
       if (lane == 0) {
 #pragma unroll
         for (int g = 0; g < kGroups; ++g)
-          if ((e >> (11 + g)) & 1) mbar_arrive(smem_u32(&fl_empty[g][gslot(g)]));
+          if ((e >> (11 + g)) & 1) mbar_arrive(smem_u32(&fl_empty[g][ej][(e >> (14 + 2 * g)) & 1]));
       }
       if (lane == 0) TST(q, 4);
       const int b_hi = (starts && !ends) ? b_last : static_cast<int>(blockIdx.x);
       bool ok = true;
-      __syncwarp();
 #pragma unroll 1
       for (int m = lane >> 4; m < M; m += 2) {
-        float v = vstage[row * 16 + m];
+        float v = vst[row * 16 + m];
         if (!starts) {
           // continuation of a tile another CTA started: store the partial sums into this
           // CTA's workspace slot (idle words read 0xffffffff); the owner polls them
@@ -513,7 +528,7 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
         }
         a.y[1ll * m * N + col] = __float2half_rn(fmaf(v, scl, bia));
       }
-      __syncwarp();  // vstage is rewritten for the next tile
+      __syncwarp();  // vst is rewritten for the next tile
       if (__any_sync(0xffffffffu, !ok)) {
         if (lane == 0) atomicExch(status, 3);
         return;
@@ -565,8 +580,9 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
 
   // Stage it goes to warp group it % kGroups; the ring depth is a multiple of kGroups, so a
   // group meets the same slots again and again and follows their barriers phase by phase.
-  float *fl_base = flush + grp * fdepth * gslot_floats + wq * kTileRows * mp;
-  int slot = grp, round = 0, fslot = 0, fround = 0;
+  float *fl_base = flush + grp * nepi * kFlushRing * gslot_floats + wq * kTileRows * mp;
+  int slot = grp, round = 0;
+  int fcnt = 0;  // hand-overs made so far to each epilogue warp: 10 bits each
   int turn = 0;  // stages this group has taken: rotates the pair ranges among its warps
 #pragma unroll 1
   for (int it = grp; it < nimg; it += kGroups, ++turn) {
@@ -577,7 +593,7 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
     }
     if (wq == 0 && lane == 0) TST(it, 1);
     const uint32_t sbase = smem_base + slot * a.slot_bytes;
-    const int c = (e >> 3) & 1023;
+    const int c = (e >> 3) & 255;
     const int fmt = e & 3;
     // inside a group the warps take turns on the pair ranges, so uneven splits average out
     const int lw = (wq + turn) & (kWarpsPerGroup - 1);
@@ -597,12 +613,17 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
     if (slot >= nst) { slot -= nst; ++round; }
 
     if (e & kEntFlush) {
-      // ---- the group's last stage of this tile: hand the partial sums to the epilogue warp
-      if (fround > 0 && !mbar_wait(smem_u32(&fl_empty[grp][fslot]), (fround - 1) & 1)) {
+      // ---- the group's last stage of this tile: hand the partial sums to the tile's epilogue
+      // warp, through the ring the two share
+      const int ej = (e >> 11) & 3;
+      const int cnt = (fcnt >> (10 * ej)) & 1023;
+      fcnt += 1 << (10 * ej);
+      const int fslot = cnt & 1, fround = cnt >> 1;
+      if (fround > 0 && !mbar_wait(smem_u32(&fl_empty[grp][ej][fslot]), (fround - 1) & 1)) {
         if (lane == 0) atomicExch(status, 5);
         return;
       }
-      float *buf = fl_base + fslot * gslot_floats;
+      float *buf = fl_base + (ej * kFlushRing + fslot) * gslot_floats;
 #pragma unroll
       for (int n = 0; n < NT; ++n) {
 #pragma unroll
@@ -615,8 +636,7 @@ __global__ void __maxnreg__(72) gemv_tiled_kernel(const __grid_constant__ TiledA
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&fl_full[grp][fslot]));
-      if (++fslot == fdepth) { fslot = 0; ++fround; }
+      if (lane == 0) mbar_arrive(smem_u32(&fl_full[grp][ej][fslot]));
     }
   }
 }
@@ -654,9 +674,9 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
   // Images are balanced by what they cost an SM, not by their bytes: the kernel is bound by
   // instruction issue, and a 16 x ck NVFP4 image (conversion + block scaling) costs more
   // than an FP8 or FP16 image of the same size (weights chosen by measurement).
-  sc.u4 = 10;
-  sc.u8 = 6;
-  sc.u16 = 5;
+  sc.u4 = RDQ_COST_U4;
+  sc.u8 = RDQ_COST_U8;
+  sc.u16 = RDQ_COST_U16;
   sc.img4 = img_bytes(0, ck);
   sc.img8 = img_bytes(1, ck);
   sc.w4 = 1ll * sc.e4 * sc.u4;
@@ -685,13 +705,12 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
   a.slot_bytes = (img_bytes(0, ck) + 127) & ~127;
   const int nt = h.M <= 8 ? 1 : 2;
   // shared memory: weight ring | flush ring | output metadata | activations (if they fit)
-  // flush rings: slots of 12 warps x 16 rows x (M rounded up to 4) partial sums, 2..8 deep
-  const int fl_slot = kMmaWarps * kTileRows * ((h.M + 3) & ~3) * 4;
-  int fdepth = 12288 / fl_slot;
-  if (fdepth > kFlushRing) fdepth = kFlushRing;
-  if (fdepth < 2) fdepth = 2;
-  a.flush_depth = fdepth;
-  const int fixed = fdepth * fl_slot + kMetaSegs * kTileRows * 12 + kMaxList * 8 + kTileRows * 16 * 4;
+  // hand-over rings: (3 groups x nepi epilogue warps) x kFlushRing slots of 4 warps x 16 rows x
+  // (M rounded up to 4) partial sums; fewer epilogue warps for large M keep this at 18-24 KB
+  const int nepi = h.M <= 4 ? kEpiWarps : (h.M <= 8 ? 2 : 1);
+  a.nepi = nepi;
+  const int fl_bytes = kGroups * nepi * kFlushRing * kWarpsPerGroup * kTileRows * ((h.M + 3) & ~3) * 4;
+  const int fixed = fl_bytes + kMetaSegs * kTileRows * 12 + kMaxList * 8 + kEpiWarps * kTileRows * 16 * 4;
   const int total_budget = 110 * 1024;  // two CTAs (this layer's and the next one's) share an SM
   int xbytes = h.M * (2 * h.K + 16);
   bool xs = true;
@@ -729,11 +748,7 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(G));
-#ifdef RDQ_TL_MONITOR
-  cfg.blockDim = dim3(kThreads + 32);  // + arrival monitor warp
-#else
   cfg.blockDim = dim3(kThreads);
-#endif
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];

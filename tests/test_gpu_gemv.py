@@ -52,6 +52,17 @@ def test_random_bytes(shape, m, flags):
     assert onp.rel_err(y, y_ref) < TOL
 
 
+@pytest.mark.parametrize("m", [1, 5, 16])
+def test_many_tiles_per_cta(m):
+    """Short rows, many channels: every CTA finishes more than 32 tiles (the segment table is
+    built in several chunks, the hand-over rings wrap many times)."""
+    n4, n8, n16, k = 60800, 20480, 5120, 256
+    layer = random_packed_layer(n4, n8, n16, k, seed=11)
+    splits = dict(zip(ORDER, (n4, n8, n16)))
+    y, y_ref, _ = _run(layer, splits, k, m, _lib.RDQ_GEMV_AUTO, bias=True, seed=m)
+    assert onp.rel_err(y, y_ref) < TOL
+
+
 def test_ragged_shapes_take_generic_kernel():
     for n4, n8, n16, k in [(49, 46, 1, 64), (0, 33, 7, 40), (5, 0, 0, 16)]:
         layer = random_packed_layer(n4, n8, n16, k, seed=7)
