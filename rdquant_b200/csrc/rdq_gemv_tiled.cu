@@ -65,6 +65,10 @@ constexpr int kThreads = (kMmaWarps + 1 + kEpiWarps) * 32;  // + producer warp +
 constexpr int kFlushRing = 2;  // slots of a hand-over ring (one per warp group and epilogue warp)
 constexpr int kMetaSegs = 32;
 constexpr int kMaxStages = 12;
+#ifndef RDQ_CHUNK_MAX
+#define RDQ_CHUNK_MAX 2048
+#endif
+constexpr int kChunkMax = RDQ_CHUNK_MAX;  // longest k chunk of an image, in NVFP4 elements
 constexpr int kMaxList = 512;       // images one CTA can stream (stage list entries)
 
 // pitch of a block-scale row inside an NVFP4 image: payload rounded up to 16 B plus a
@@ -85,7 +89,7 @@ __host__ __device__ inline int img_bytes(int fmt, int ck) {
 // the smallest number of chunks n with K/n <= 2048 and K/n a multiple of 64.
 int tiled_chunk_k(int K) {
   if (K <= 0 || K % 64 != 0) return 0;
-  for (int n = (K + 2047) / 2048; n <= K / 64; ++n) {
+  for (int n = (K + kChunkMax - 1) / kChunkMax; n <= K / 64; ++n) {
     if (K % n == 0 && (K / n) % 64 == 0) return K / n;
   }
   return 0;
