@@ -42,7 +42,7 @@ namespace {
 
 constexpr int BM = 128, BN = 128, BK = 64;
 constexpr int kStages = 4;
-constexpr int kProducerWarps = 7;
+constexpr int kProducerWarps = 14;  // two threads per weight row (128 rows padded per format to 16)
 constexpr int kProducers = kProducerWarps * 32;
 constexpr int kGemmThreads = (2 + kProducerWarps) * 32;
 constexpr int kStageA = BM * BK * 2;  // 16 KB

@@ -16,91 +16,96 @@ __device__ int g_gemm_aborts;  // launches that hit a bounded-wait timeout (diag
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");                      \
   mbar_arrive(smem_u32(&S.full[s]));
 
-__device__ __forceinline__ void produce_fp4(GemmSmem &S, const GemmArgs &a, uint32_t b_base, int j, int r, int nkb) {
+// A thread owns HALF a weight row of the tile (32 of the 64 k of a block: chunks 4h .. 4h+3).
+__device__ __forceinline__ uint32_t ldg_nc2(const void *p) {
+  uint16_t v;
+  asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void produce_fp4(GemmSmem &S, const GemmArgs &a, uint32_t b_base, int j, int h, int r, int nkb) {
   const uint32_t row_off = (j >> 3) * 1024 + (j & 7) * 128;
   const int sw = j & 7;
-  const uint8_t *wp = a.w4 + 1ll * r * (a.K >> 1);
-  const uint8_t *sp = a.s4 + 1ll * r * (a.K >> 4);
+  const uint8_t *wp = a.w4 + 1ll * r * (a.K >> 1) + h * 16;
+  const uint8_t *sp = a.s4 + 1ll * r * (a.K >> 4) + h * 2;
   bool alive = true;
-  uint4 q0 = ldg_nc16(wp), q1 = ldg_nc16(wp + 16);
-  uint32_t sc = ldg_nc4(sp);
+  uint4 q0 = ldg_nc16(wp);
+  uint32_t sc = ldg_nc2(sp);
   for (int kb = 0; kb < nkb; ++kb) {
-    const uint4 c0 = q0, c1 = q1;
+    const uint4 c0 = q0;
     const uint32_t csc = sc;
     if (kb + 1 < nkb) {
       q0 = ldg_nc16(wp + (kb + 1) * 32);
-      q1 = ldg_nc16(wp + (kb + 1) * 32 + 16);
-      sc = ldg_nc4(sp + (kb + 1) * 4);
+      sc = ldg_nc2(sp + (kb + 1) * 4);
     }
     RDQ_STAGE_BEGIN(kb)
-    const uint32_t s01 = cvt_e4m3x2(csc), s23 = cvt_e4m3x2(csc >> 16);
-    const uint32_t sb[4] = {__byte_perm(s01, 0u, 0x1010u), __byte_perm(s01, 0u, 0x3232u),
-                            __byte_perm(s23, 0u, 0x1010u), __byte_perm(s23, 0u, 0x3232u)};
-    const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const uint32_t s01 = cvt_e4m3x2(csc);
+    const uint32_t sb[2] = {__byte_perm(s01, 0u, 0x1010u), __byte_perm(s01, 0u, 0x3232u)};
+    const uint32_t w[4] = {c0.x, c0.y, c0.z, c0.w};
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
+    for (int c = 0; c < 4; ++c) {
       uint32_t h0, h1, h2, h3;
       cvt_e2m1x8(w[c], h0, h1, h2, h3);
       const uint32_t scl = sb[c >> 1];
-      st_chunk(row_base, sw, c, hmul2_u32(h0, scl), hmul2_u32(h1, scl), hmul2_u32(h2, scl), hmul2_u32(h3, scl));
+      st_chunk(row_base, sw, 4 * h + c, hmul2_u32(h0, scl), hmul2_u32(h1, scl), hmul2_u32(h2, scl), hmul2_u32(h3, scl));
     }
     RDQ_STAGE_END()
   }
 }
 
-__device__ __forceinline__ void produce_fp8(GemmSmem &S, const GemmArgs &a, uint32_t b_base, int j, int r, int nkb) {
+__device__ __forceinline__ void produce_fp8(GemmSmem &S, const GemmArgs &a, uint32_t b_base, int j, int h, int r, int nkb) {
   const uint32_t row_off = (j >> 3) * 1024 + (j & 7) * 128;
   const int sw = j & 7;
-  const uint8_t *wp = a.w8 + 1ll * (r - a.n4) * a.K;
+  const uint8_t *wp = a.w8 + 1ll * (r - a.n4) * a.K + h * 32;
   bool alive = true;
-  uint4 q[4];
+  uint4 q[2];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) q[i] = ldg_nc16(wp + 16 * i);
+  for (int i = 0; i < 2; ++i) q[i] = ldg_nc16(wp + 16 * i);
   for (int kb = 0; kb < nkb; ++kb) {
-    uint4 c[4];
+    uint4 c[2];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) c[i] = q[i];
+    for (int i = 0; i < 2; ++i) c[i] = q[i];
     if (kb + 1 < nkb) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) q[i] = ldg_nc16(wp + (kb + 1) * 64 + 16 * i);
+      for (int i = 0; i < 2; ++i) q[i] = ldg_nc16(wp + (kb + 1) * 64 + 16 * i);
     }
     RDQ_STAGE_BEGIN(kb)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 2; ++i) {
       uint32_t h0, h1, h2, h3, h4, h5, h6, h7;
       cvt_e4m3x4(c[i].x, h0, h1);
       cvt_e4m3x4(c[i].y, h2, h3);
       cvt_e4m3x4(c[i].z, h4, h5);
       cvt_e4m3x4(c[i].w, h6, h7);
-      st_chunk(row_base, sw, 2 * i, h0, h1, h2, h3);
-      st_chunk(row_base, sw, 2 * i + 1, h4, h5, h6, h7);
+      st_chunk(row_base, sw, 4 * h + 2 * i, h0, h1, h2, h3);
+      st_chunk(row_base, sw, 4 * h + 2 * i + 1, h4, h5, h6, h7);
     }
     RDQ_STAGE_END()
   }
 }
 
 // FP16 rows, rows beyond N (r < 0: zeros) and idle padding threads (j < 0: only the barrier protocol)
-__device__ __forceinline__ void produce_fp16(GemmSmem &S, const GemmArgs &a, uint32_t b_base, int j, int r, int nkb) {
+__device__ __forceinline__ void produce_fp16(GemmSmem &S, const GemmArgs &a, uint32_t b_base, int j, int h, int r, int nkb) {
   const uint32_t row_off = j >= 0 ? (j >> 3) * 1024 + (j & 7) * 128 : 0;
   const int sw = j & 7;
   const bool real = (j >= 0) && (r >= 0);
-  const __half *wp = real ? a.w16 + 1ll * (r - a.n4 - a.n8) * a.K : nullptr;
+  const __half *wp = real ? a.w16 + 1ll * (r - a.n4 - a.n8) * a.K + h * 32 : nullptr;
   bool alive = true;
-  uint4 q[8];
+  uint4 q[4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) q[i] = real ? ldg_nc16(wp + 8 * i) : make_uint4(0u, 0u, 0u, 0u);
+  for (int i = 0; i < 4; ++i) q[i] = real ? ldg_nc16(wp + 8 * i) : make_uint4(0u, 0u, 0u, 0u);
   for (int kb = 0; kb < nkb; ++kb) {
-    uint4 c[8];
+    uint4 c[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) c[i] = q[i];
+    for (int i = 0; i < 4; ++i) c[i] = q[i];
     if (real && kb + 1 < nkb) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) q[i] = ldg_nc16(wp + (kb + 1) * 64 + 8 * i);
+      for (int i = 0; i < 4; ++i) q[i] = ldg_nc16(wp + (kb + 1) * 64 + 8 * i);
     }
     RDQ_STAGE_BEGIN(kb)
     if (j >= 0) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) st_chunk(row_base, sw, i, c[i].x, c[i].y, c[i].z, c[i].w);
+      for (int i = 0; i < 4; ++i) st_chunk(row_base, sw, 4 * h + i, c[i].x, c[i].y, c[i].z, c[i].w);
     }
     RDQ_STAGE_END()
   }
@@ -221,22 +226,23 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------- weight dequantisation
-    const int pt = tid - 64;
+    // two threads per weight row (k halves); each format's rows are padded to whole warps
+    const int pt = (tid - 64) >> 1, h = tid & 1;
     const int c0 = S.count[0], c1 = S.count[1], c2 = S.count[2];
-    const int start1 = (c0 + 31) & ~31, start2 = start1 + ((c1 + 31) & ~31);
+    const int start1 = (c0 + 15) & ~15, start2 = start1 + ((c1 + 15) & ~15);
     if (pt < start1) {
       const int j = pt < c0 ? S.order[0][pt] : -1;
-      if (j >= 0) produce_fp4(S, a, b_base, j, S.row_perm[j], nkb);
-      else produce_fp16(S, a, b_base, -1, -1, nkb);
+      if (j >= 0) produce_fp4(S, a, b_base, j, h, S.row_perm[j], nkb);
+      else produce_fp16(S, a, b_base, -1, h, -1, nkb);
     } else if (pt < start2) {
       const int idx = pt - start1;
       const int j = idx < c1 ? S.order[1][idx] : -1;
-      if (j >= 0) produce_fp8(S, a, b_base, j, S.row_perm[j], nkb);
-      else produce_fp16(S, a, b_base, -1, -1, nkb);
+      if (j >= 0) produce_fp8(S, a, b_base, j, h, S.row_perm[j], nkb);
+      else produce_fp16(S, a, b_base, -1, h, -1, nkb);
     } else {
       const int idx = pt - start2;
       const int j = idx < c2 ? S.order[2][idx] : -1;
-      produce_fp16(S, a, b_base, j, j >= 0 ? S.row_perm[j] : -1, nkb);
+      produce_fp16(S, a, b_base, j, h, j >= 0 ? S.row_perm[j] : -1, nkb);
     }
 
     // ----------------------------------------------------------------------- epilogue
