@@ -40,28 +40,42 @@ namespace rdq {
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64;
-constexpr int kStages = 4;
-constexpr int kProducerWarps = 14;  // two threads per weight row (128 rows padded per format to 16)
-constexpr int kProducers = kProducerWarps * 32;
-constexpr int kGemmThreads = (2 + kProducerWarps) * 32;
-constexpr int kStageA = BM * BK * 2;  // 16 KB
-constexpr int kStageB = BN * BK * 2;  // 16 KB
-constexpr int kTmemCols = 128;
+constexpr int BM = 128, BK = 64;
+constexpr int kStageA = BM * BK * 2;  // 16 KB: one 128-token activation block
+constexpr int kMaxBN = 256;
+
+// Tile configurations.  BN = output channels per CTA (= N of one tcgen05.mma), MT = 128-token
+// accumulators per CTA.  Producer warps convert groups of four weight rows (a quarter warp per
+// row); kTasks = groups a warp handles per k block.
+//   <1,128> <2,128>: 12 producer warps, 4 stages         (small problems)
+//   <2,256>        : 14 producer warps, 3 x 64 KB stages, all 512 tensor-memory columns
+template <int MT, int BN>
+struct GemmCfg {
+  static constexpr int kProducerWarps = (BN == 128) ? 12 : 14;
+  static constexpr int kProducers = kProducerWarps * 32;
+  static constexpr int kThreads = (2 + kProducerWarps) * 32;
+  static constexpr int kStageB = BN * BK * 2;
+  static constexpr int kStageAll = kStageA * MT;
+  static constexpr int kStages = (BN == 128) ? 4 : 3;
+  static constexpr int kTmemCols = BN * MT;  // power of two >= 32
+  static constexpr int kSmem = kStages * (kStageAll + kStageB) + 1024;
+  static constexpr int kMaxQuads = BN / 4 + 3;  // each format padded to a multiple of four rows
+  static constexpr int kTasks = (kMaxQuads + kProducerWarps - 1) / kProducerWarps;
+};
 
 struct GemmSmem {
   // dynamic part starts 1024-byte aligned: A stages, then B stages
   // static part:
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[4];
+  uint64_t empty[4];
   uint64_t accum;
   uint32_t tmem_base;
   int abort_flag;
-  int row_perm[BN];       // permuted row of tile row j, or -1
-  int order[3][BN];       // tile rows of each format, in tile order
-  int count[3];
-  float colscale[BN];
-  float colbias[BN];
+  int row_perm[kMaxBN];       // permuted row of tile row j, or -1
+  int prow[kMaxBN + 12];      // tile rows sorted by format, each format padded to four (-1)
+  int nquad;                  // groups of four rows in prow
+  float colscale[kMaxBN];
+  float colbias[kMaxBN];
 };
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
@@ -100,10 +114,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
-}
-__device__ __forceinline__ void st_chunk(uint32_t row_base, int sw, int c, uint32_t a, uint32_t b, uint32_t cc, uint32_t d) {
-  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(row_base + ((c ^ sw) << 4)), "r"(a), "r"(b), "r"(cc), "r"(d)
-               : "memory");
 }
 __device__ __forceinline__ uint4 ldg_nc16(const void *p) {
   uint4 v;

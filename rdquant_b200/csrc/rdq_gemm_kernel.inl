@@ -5,124 +5,159 @@ namespace {
 
 __device__ int g_gemm_aborts;  // launches that hit a bounded-wait timeout (diagnostic counter)
 
-// ---- dequantisation loops: one thread = one weight row of the tile, all k blocks --------
-// Common stage protocol: wait until the MMA has released stage s, write the row, make the
-// generic-proxy writes visible to the async proxy, arrive on full[s].
-#define RDQ_STAGE_BEGIN(kb)                                                         \
-  const int s = (kb) & (kStages - 1);                                               \
-  if ((kb) >= kStages && alive) alive = gemm_wait(&S.empty[s], (((kb) / kStages) - 1) & 1, &S.abort_flag); \
-  const uint32_t row_base = b_base + s * kStageB + row_off;
-#define RDQ_STAGE_END()                                                             \
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");                      \
-  mbar_arrive(smem_u32(&S.full[s]));
+#ifdef RDQ_GEMM_TIMELINE
+// debug build: per-k-block clocks of CTA (1, 1): [kb][0] MMA warp starts waiting, [1] stage full,
+// [2] MMAs issued; [3] producer thread 0 starts waiting for the empty stage, [4] got it, [5] arrived
+__device__ long long g_gtl[128 * 8];
+#define GTL(kb_, col_) do { if (blockIdx.x == 1 && blockIdx.y == 1 && (kb_) < 128) g_gtl[(kb_) * 8 + (col_)] = clock64(); } while (0)
+#else
+#define GTL(kb_, col_) do { } while (0)
+#endif
 
-// A thread owns HALF a weight row of the tile (32 of the 64 k of a block: chunks 4h .. 4h+3).
 __device__ __forceinline__ uint32_t ldg_nc2(const void *p) {
   uint16_t v;
   asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
   return v;
 }
 
-__device__ __forceinline__ void produce_fp4(GemmSmem &S, const GemmArgs &a, uint32_t b_base, int j, int h, int r, int nkb) {
-  const uint32_t row_off = (j >> 3) * 1024 + (j & 7) * 128;
-  const int sw = j & 7;
-  const uint8_t *wp = a.w4 + 1ll * r * (a.K >> 1) + h * 16;
-  const uint8_t *sp = a.s4 + 1ll * r * (a.K >> 4) + h * 2;
+// Stage bookkeeping of one producer thread: before writing stage s of round ph it waits until
+// the MMA has released it; afterwards it makes its generic-proxy writes visible to the async
+// proxy and arrives on full[s].
+template <int NS>
+struct StageCursor {
+  int s = 0, ph = 0;
   bool alive = true;
-  uint4 q0 = ldg_nc16(wp);
-  uint32_t sc = ldg_nc2(sp);
+  __device__ __forceinline__ void begin(GemmSmem &S) {
+    if (ph > 0 && alive) alive = gemm_wait(&S.empty[s], (ph - 1) & 1, &S.abort_flag);
+  }
+  __device__ __forceinline__ void end(GemmSmem &S) {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_arrive(smem_u32(&S.full[s]));
+    if (++s == NS) { s = 0; ++ph; }
+  }
+};
+
+// ---- dequantisation: eight lanes share one weight row of the tile, one 16-byte chunk (8 k)
+// each, so that a quarter warp writes the 128 contiguous (swizzled) bytes of a row and reads
+// 32 / 64 / 128 contiguous packed bytes.  The tile's rows are sorted by format and padded to
+// groups of four (one group per warp and step); a warp takes every W-th group.
+__device__ __forceinline__ uint32_t ldg_nc1(const void *p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ldg_nc8(const void *p) {
+  uint2 v;
+  asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+
+template <int NS, int SB, int TMAX>
+__device__ __forceinline__ void produce_rows(GemmSmem &S, const GemmArgs &a, uint32_t b_base, int pwarp, int nwarps,
+                                             int lane, int nkb) {
+  const int chunk = lane & 7, sub = lane >> 3;
+  const int nq = S.nquad;
+  // per task: packed-byte pointer (already at this lane's chunk), scale pointer (NVFP4), row
+  // offset inside a stage, swizzle key, format (3 = write zeros, 4 = nothing to do)
+  const uint8_t *wp[TMAX];
+  const uint8_t *sp[TMAX];
+  uint32_t roff[TMAX];
+  int fmt[TMAX];
+#pragma unroll
+  for (int t = 0; t < TMAX; ++t) {
+    const int quad = pwarp + t * nwarps;
+    fmt[t] = 4;
+    wp[t] = nullptr;
+    sp[t] = nullptr;
+    roff[t] = 0;
+    if (quad < nq) {
+      const int j = S.prow[quad * 4 + sub];
+      if (j >= 0) {
+        const int r = S.row_perm[j];
+        roff[t] = (j >> 3) * 1024 + (j & 7) * 128 + ((chunk ^ (j & 7)) << 4);
+        if (r < 0) {
+          fmt[t] = 3;
+        } else if (r < a.n4) {
+          fmt[t] = 0;
+          wp[t] = a.w4 + 1ll * r * (a.K >> 1) + chunk * 4;
+          sp[t] = a.s4 + 1ll * r * (a.K >> 4) + (chunk >> 1);
+        } else if (r < a.n4 + a.n8) {
+          fmt[t] = 1;
+          wp[t] = a.w8 + 1ll * (r - a.n4) * a.K + chunk * 8;
+        } else {
+          fmt[t] = 2;
+          wp[t] = reinterpret_cast<const uint8_t *>(a.w16 + 1ll * (r - a.n4 - a.n8) * a.K) + chunk * 16;
+        }
+      }
+    }
+  }
+  auto load = [&](int t, int kb) {
+    uint4 d = make_uint4(0u, 0u, 0u, 0u);
+    if (fmt[t] == 0) {
+      d.x = ldg_nc4(wp[t] + kb * 32);
+      d.y = ldg_nc1(sp[t] + kb * 4);
+    } else if (fmt[t] == 1) {
+      const uint2 v = ldg_nc8(wp[t] + kb * 64);
+      d.x = v.x;
+      d.y = v.y;
+    } else if (fmt[t] == 2) {
+      d = ldg_nc16(wp[t] + kb * 128);
+    }
+    return d;
+  };
+  StageCursor<NS> cur;
+  uint4 q[TMAX];
+#pragma unroll
+  for (int t = 0; t < TMAX; ++t) q[t] = load(t, 0);
   for (int kb = 0; kb < nkb; ++kb) {
-    const uint4 c0 = q0;
-    const uint32_t csc = sc;
+    uint4 c[TMAX];
+#pragma unroll
+    for (int t = 0; t < TMAX; ++t) c[t] = q[t];
     if (kb + 1 < nkb) {
-      q0 = ldg_nc16(wp + (kb + 1) * 32);
-      sc = ldg_nc2(sp + (kb + 1) * 4);
-    }
-    RDQ_STAGE_BEGIN(kb)
-    const uint32_t s01 = cvt_e4m3x2(csc);
-    const uint32_t sb[2] = {__byte_perm(s01, 0u, 0x1010u), __byte_perm(s01, 0u, 0x3232u)};
-    const uint32_t w[4] = {c0.x, c0.y, c0.z, c0.w};
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t h0, h1, h2, h3;
-      cvt_e2m1x8(w[c], h0, h1, h2, h3);
-      const uint32_t scl = sb[c >> 1];
-      st_chunk(row_base, sw, 4 * h + c, hmul2_u32(h0, scl), hmul2_u32(h1, scl), hmul2_u32(h2, scl), hmul2_u32(h3, scl));
+      for (int t = 0; t < TMAX; ++t) q[t] = load(t, kb + 1);
     }
-    RDQ_STAGE_END()
+    if (threadIdx.x == 64) GTL(kb, 3);
+    cur.begin(S);
+    if (threadIdx.x == 64) GTL(kb, 4);
+    const uint32_t sbase = b_base + cur.s * SB;
+#pragma unroll
+    for (int t = 0; t < TMAX; ++t) {
+      uint32_t o0 = 0u, o1 = 0u, o2 = 0u, o3 = 0u;
+      if (fmt[t] == 0) {
+        const uint32_t scl = __byte_perm(cvt_e4m3x2(c[t].y), 0u, 0x1010u);
+        cvt_e2m1x8(c[t].x, o0, o1, o2, o3);
+        o0 = hmul2_u32(o0, scl);
+        o1 = hmul2_u32(o1, scl);
+        o2 = hmul2_u32(o2, scl);
+        o3 = hmul2_u32(o3, scl);
+      } else if (fmt[t] == 1) {
+        cvt_e4m3x4(c[t].x, o0, o1);
+        cvt_e4m3x4(c[t].y, o2, o3);
+      } else if (fmt[t] == 2) {
+        o0 = c[t].x; o1 = c[t].y; o2 = c[t].z; o3 = c[t].w;
+      }
+      if (fmt[t] != 4)
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sbase + roff[t]), "r"(o0), "r"(o1), "r"(o2), "r"(o3)
+                     : "memory");
+    }
+    cur.end(S);
+    if (threadIdx.x == 64) GTL(kb, 5);
   }
 }
 
-__device__ __forceinline__ void produce_fp8(GemmSmem &S, const GemmArgs &a, uint32_t b_base, int j, int h, int r, int nkb) {
-  const uint32_t row_off = (j >> 3) * 1024 + (j & 7) * 128;
-  const int sw = j & 7;
-  const uint8_t *wp = a.w8 + 1ll * (r - a.n4) * a.K + h * 32;
-  bool alive = true;
-  uint4 q[2];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) q[i] = ldg_nc16(wp + 16 * i);
-  for (int kb = 0; kb < nkb; ++kb) {
-    uint4 c[2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) c[i] = q[i];
-    if (kb + 1 < nkb) {
-#pragma unroll
-      for (int i = 0; i < 2; ++i) q[i] = ldg_nc16(wp + (kb + 1) * 64 + 16 * i);
-    }
-    RDQ_STAGE_BEGIN(kb)
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      uint32_t h0, h1, h2, h3, h4, h5, h6, h7;
-      cvt_e4m3x4(c[i].x, h0, h1);
-      cvt_e4m3x4(c[i].y, h2, h3);
-      cvt_e4m3x4(c[i].z, h4, h5);
-      cvt_e4m3x4(c[i].w, h6, h7);
-      st_chunk(row_base, sw, 4 * h + 2 * i, h0, h1, h2, h3);
-      st_chunk(row_base, sw, 4 * h + 2 * i + 1, h4, h5, h6, h7);
-    }
-    RDQ_STAGE_END()
-  }
-}
-
-// FP16 rows, rows beyond N (r < 0: zeros) and idle padding threads (j < 0: only the barrier protocol)
-__device__ __forceinline__ void produce_fp16(GemmSmem &S, const GemmArgs &a, uint32_t b_base, int j, int h, int r, int nkb) {
-  const uint32_t row_off = j >= 0 ? (j >> 3) * 1024 + (j & 7) * 128 : 0;
-  const int sw = j & 7;
-  const bool real = (j >= 0) && (r >= 0);
-  const __half *wp = real ? a.w16 + 1ll * (r - a.n4 - a.n8) * a.K + h * 32 : nullptr;
-  bool alive = true;
-  uint4 q[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) q[i] = real ? ldg_nc16(wp + 8 * i) : make_uint4(0u, 0u, 0u, 0u);
-  for (int kb = 0; kb < nkb; ++kb) {
-    uint4 c[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) c[i] = q[i];
-    if (real && kb + 1 < nkb) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) q[i] = ldg_nc16(wp + (kb + 1) * 64 + 8 * i);
-    }
-    RDQ_STAGE_BEGIN(kb)
-    if (j >= 0) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) st_chunk(row_base, sw, 4 * h + i, c[i].x, c[i].y, c[i].z, c[i].w);
-    }
-    RDQ_STAGE_END()
-  }
-}
-
-// MT = 128-token accumulators per CTA (1 or 2): with MT = 2 one dequantised weight stage
-// feeds two MMAs groups, halving the conversion work per flop.
-template <int MT>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int MT, int BN>
+__global__ void __launch_bounds__(GemmCfg<MT, BN>::kThreads, 1)
 gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ GemmArgs a) {
-  constexpr int kStageAll = kStageA * MT;
-  constexpr uint32_t kCols = kTmemCols * MT;
+  using Cfg = GemmCfg<MT, BN>;
+  constexpr int NS = Cfg::kStages, SB = Cfg::kStageB;
+  constexpr int kStageAll = Cfg::kStageAll;
+  constexpr uint32_t kCols = Cfg::kTmemCols;
   extern __shared__ uint8_t smem_raw[];
   __shared__ GemmSmem S;
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t a_base = (raw_addr + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
-  const uint32_t b_base = a_base + kStages * kStageAll;
+  const uint32_t b_base = a_base + NS * kStageAll;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -133,8 +168,8 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
   const int nkb = a.K / BK;
 
   if (tid == 0) {
-    for (int i = 0; i < kStages; ++i) {
-      mbar_init(smem_u32(&S.full[i]), kProducers + 1);
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(smem_u32(&S.full[i]), Cfg::kProducers + 1);
       mbar_init(smem_u32(&S.empty[i]), 1);
     }
     mbar_init(smem_u32(&S.accum), 1);
@@ -147,8 +182,7 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  if (tid >= 64 && tid < 64 + BN) {
-    const int j = tid - 64;
+  for (int j = tid - 64; j >= 0 && j < BN; j += Cfg::kProducers) {
     const int n = n0 + j;
     int r = -1;
     float scl = 0.f, bia = 0.f;
@@ -163,24 +197,24 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
   }
   __syncthreads();
   if (warp == 2) {
-    // sort the tile rows by format (stable), one list per format
-    int cnt[3] = {0, 0, 0};
-    for (int round = 0; round < BN / 32; ++round) {
-      const int j = round * 32 + lane;
-      const int r = S.row_perm[j];
-      const int f = (r >= 0 && r < a.n4) ? 0 : ((r >= a.n4 && r < a.n4 + a.n8) ? 1 : 2);
-#pragma unroll
-      for (int ff = 0; ff < 3; ++ff) {
+    // sort the tile rows by format (stable); each format's rows are padded to groups of four
+    int base = 0;
+#pragma unroll 1
+    for (int ff = 0; ff < 3; ++ff) {
+      int cnt = 0;
+      for (int round = 0; round < BN / 32; ++round) {
+        const int j = round * 32 + lane;
+        const int r = S.row_perm[j];
+        const int f = (r >= 0 && r < a.n4) ? 0 : ((r >= a.n4 && r < a.n4 + a.n8) ? 1 : 2);
         const uint32_t mask = __ballot_sync(0xffffffffu, f == ff);
-        if (f == ff) S.order[ff][cnt[ff] + __popc(mask & ((1u << lane) - 1u))] = j;
-        cnt[ff] += __popc(mask);
+        if (f == ff) S.prow[base + cnt + __popc(mask & ((1u << lane) - 1u))] = j;
+        cnt += __popc(mask);
       }
+      const int padded = (cnt + 3) & ~3;
+      if (lane < padded - cnt) S.prow[base + cnt + lane] = -1;
+      base += padded;
     }
-    if (lane == 0) {
-      S.count[0] = cnt[0];
-      S.count[1] = cnt[1];
-      S.count[2] = cnt[2];
-    }
+    if (lane == 0) S.nquad = base >> 2;
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -191,15 +225,20 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
     // ------------------------------------------------------------- activation loads (TMA)
     if (lane == 0) {
       bool alive = true;
+      int s = 0, ph = 0;
       for (int kb = 0; kb < nkb && alive; ++kb) {
-        const int s = kb & (kStages - 1);
-        if (kb >= kStages) alive = gemm_wait(&S.empty[s], ((kb / kStages) - 1) & 1, &S.abort_flag);
+        if (ph > 0) alive = gemm_wait(&S.empty[s], (ph - 1) & 1, &S.abort_flag);
         if (!alive) break;
         const uint32_t full = smem_u32(&S.full[s]);
+#ifdef RDQ_GEMM_SKIP_TMA  // debug experiment: no activation loads (results are wrong)
+        mbar_arrive(full);
+#else
         mbar_arrive_expect_tx(full, kStageAll);
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
           tma_load_2d(a_base + s * kStageAll + mt * kStageA, &xmap, kb * BK, m0 + mt * BM, full);
+#endif
+        if (++s == NS) { s = 0; ++ph; }
       }
     }
   } else if (warp == 1) {
@@ -207,56 +246,47 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
     if (lane == 0) {
       constexpr uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
       bool alive = true;
+      int s = 0, ph = 0;
       for (int kb = 0; kb < nkb && alive; ++kb) {
-        const int s = kb & (kStages - 1);
-        alive = gemm_wait(&S.full[s], (kb / kStages) & 1, &S.abort_flag);
+        GTL(kb, 0);
+        alive = gemm_wait(&S.full[s], ph & 1, &S.abort_flag);
         if (!alive) break;
+        GTL(kb, 1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t db = make_desc_sw128(b_base + s * kStageB);
+        const uint64_t db = make_desc_sw128(b_base + s * SB);
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           const uint64_t da = make_desc_sw128(a_base + s * kStageAll + mt * kStageA);
 #pragma unroll
           for (int k4 = 0; k4 < BK / 16; ++k4)
-            umma_f16(tmem + mt * kTmemCols, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0 ? 1u : 0u);
+            umma_f16(tmem + mt * BN, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0 ? 1u : 0u);
         }
         umma_commit(smem_u32(&S.empty[s]));
+        GTL(kb, 2);
+        if (++s == NS) { s = 0; ++ph; }
       }
       umma_commit(smem_u32(&S.accum));
     }
   } else {
     // ------------------------------------------------------------- weight dequantisation
-    // two threads per weight row (k halves); each format's rows are padded to whole warps
-    const int pt = (tid - 64) >> 1, h = tid & 1;
-    const int c0 = S.count[0], c1 = S.count[1], c2 = S.count[2];
-    const int start1 = (c0 + 15) & ~15, start2 = start1 + ((c1 + 15) & ~15);
-    if (pt < start1) {
-      const int j = pt < c0 ? S.order[0][pt] : -1;
-      if (j >= 0) produce_fp4(S, a, b_base, j, h, S.row_perm[j], nkb);
-      else produce_fp16(S, a, b_base, -1, h, -1, nkb);
-    } else if (pt < start2) {
-      const int idx = pt - start1;
-      const int j = idx < c1 ? S.order[1][idx] : -1;
-      if (j >= 0) produce_fp8(S, a, b_base, j, h, S.row_perm[j], nkb);
-      else produce_fp16(S, a, b_base, -1, h, -1, nkb);
-    } else {
-      const int idx = pt - start2;
-      const int j = idx < c2 ? S.order[2][idx] : -1;
-      produce_fp16(S, a, b_base, j, h, j >= 0 ? S.row_perm[j] : -1, nkb);
-    }
+    produce_rows<NS, SB, Cfg::kTasks>(S, a, b_base, warp - 2, Cfg::kProducerWarps, lane, nkb);
 
     // ----------------------------------------------------------------------- epilogue
-    if (warp >= 2 && warp < 6) {
+    // A warp may read the tensor-memory lanes 32 (warp % 4) ...; the producer warps that share a
+    // lane quarter take the 32-column chunks of the accumulators in turn.
+    constexpr int kEpiWarps = (Cfg::kProducerWarps / 4) * 4;  // whole sets of four warps
+    if (warp - 2 < kEpiWarps) {
       const bool ok = gemm_wait(&S.accum, 0, &S.abort_flag);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+      const int sub = (warp - 2) >> 2;
       if (ok) {
 #pragma unroll 1
-        for (int ci = 0; ci < MT * (BN / 32); ++ci) {
+        for (int ci = sub; ci < MT * (BN / 32); ci += kEpiWarps / 4) {
           const int mt = ci / (BN / 32), cc = ci % (BN / 32);
           const int m = m0 + mt * BM + q * 32 + lane;
           uint32_t r[32];
-          tmem_ld32(tmem + (static_cast<uint32_t>(q * 32) << 16) + mt * kTmemCols + cc * 32, r);
+          tmem_ld32(tmem + (static_cast<uint32_t>(q * 32) << 16) + mt * BN + cc * 32, r);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           if (m < a.M) {
             __half *dst = a.y + 1ll * m * N + n0 + cc * 32;
@@ -299,7 +329,29 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+template <int MT, int BN>
+int launch_cfg(const CUtensorMap &xmap, const GemmArgs &a, int N, cudaStream_t stream) {
+  using Cfg = GemmCfg<MT, BN>;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  RDQ_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_done[dev]) {
+    RDQ_CUDA(cudaFuncSetAttribute(gemm_mixed_kernel<MT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+    attr_done[dev] = true;
+  }
+  const dim3 grid((a.M + MT * BM - 1) / (MT * BM), (N + BN - 1) / BN);
+  gemm_mixed_kernel<MT, BN><<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(xmap, a);
+  RDQ_CUDA(cudaGetLastError());
+  return RDQ_OK;
+}
+
 }  // namespace
+
+#ifdef RDQ_GEMM_TIMELINE
+extern "C" int rdq_debug_gemm_timeline(long long *host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_gtl, sizeof(long long) * 128 * 8) == cudaSuccess ? 0 : -3;
+}
+#endif
 
 int launch_gemm(const GemmArgs &a, cudaStream_t stream) {
   static EncodeTiledFn encode = nullptr;
@@ -309,16 +361,6 @@ int launch_gemm(const GemmArgs &a, cudaStream_t stream) {
     RDQ_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr));
     RDQ_REQUIRE(fn != nullptr && qr == cudaDriverEntryPointSuccess, RDQ_E_CUDA, "cuTensorMapEncodeTiled is not available");
     encode = reinterpret_cast<EncodeTiledFn>(fn);
-  }
-  static bool attr_done[64] = {};
-  int dev = 0;
-  RDQ_CUDA(cudaGetDevice(&dev));
-  const int smem1 = kStages * (kStageA + kStageB) + 1024;
-  const int smem2 = kStages * (2 * kStageA + kStageB) + 1024;
-  if (dev < 64 && !attr_done[dev]) {
-    RDQ_CUDA(cudaFuncSetAttribute(gemm_mixed_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1));
-    RDQ_CUDA(cudaFuncSetAttribute(gemm_mixed_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
-    attr_done[dev] = true;
   }
   const int N = a.n4 + a.n8 + a.n16;
   CUtensorMap xmap;
@@ -330,18 +372,13 @@ int launch_gemm(const GemmArgs &a, cudaStream_t stream) {
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   RDQ_REQUIRE(rc == CUDA_SUCCESS, RDQ_E_CUDA, "cuTensorMapEncodeTiled failed with code %d", static_cast<int>(rc));
-  // 256-token tiles once there are enough of them to fill the GPU
-  const int ntile_n = (N + BN - 1) / BN;
-  const bool two = ((a.M + 2 * BM - 1) / (2 * BM)) * ntile_n >= sm_count();
-  if (two) {
-    const dim3 grid((a.M + 2 * BM - 1) / (2 * BM), ntile_n);
-    gemm_mixed_kernel<2><<<grid, kGemmThreads, smem2, stream>>>(xmap, a);
-  } else {
-    const dim3 grid((a.M + BM - 1) / BM, ntile_n);
-    gemm_mixed_kernel<1><<<grid, kGemmThreads, smem1, stream>>>(xmap, a);
-  }
-  RDQ_CUDA(cudaGetLastError());
-  return RDQ_OK;
+  // the largest tile that still gives every SM a CTA: 256 tokens x 256 channels, 256 x 128, 128 x 128
+  const int sms = sm_count();
+  const int t256 = (a.M + 255) / 256, t128 = (a.M + 127) / 128;
+  if (t256 * ((N + 255) / 256) >= sms) return launch_cfg<2, 256>(xmap, a, N, stream);
+  if (t256 * ((N + 127) / 128) >= sms) return launch_cfg<2, 128>(xmap, a, N, stream);
+  (void)t128;
+  return launch_cfg<1, 128>(xmap, a, N, stream);
 }
 
 }  // namespace rdq

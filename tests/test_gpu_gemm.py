@@ -72,3 +72,17 @@ def test_matches_dequantised_weight_matmul():
     ref = x.float() @ w.float().T
     err = (y.float() - ref).abs().max() / ref.abs().max()
     assert float(err) < TOL
+
+
+@pytest.mark.parametrize("m,n,k", [(1024, 9728, 256), (1000, 9800, 192), (4096, 2560, 320)])
+def test_large_tiles(m, n, k):
+    """Enough tiles to select the 256-token x 256-channel configuration (all tensor-memory
+    columns, three 64 KB stages), with ragged M and N, against the oracle and against
+    x @ dequant(W)^T."""
+    n16 = 128
+    n8 = (n // 3) // 128 * 128
+    n4 = n - n8 - n16
+    layer = random_packed_layer(n4, n8, n16, k, seed=m + k)
+    splits = dict(zip(ORDER, (n4, n8, n16)))
+    y, y_ref = _run(layer, splits, k, m, bias=True, seed=5)
+    assert onp.rel_err(y, y_ref) < TOL
