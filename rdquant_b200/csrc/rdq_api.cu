@@ -216,6 +216,9 @@ int rdq_gemm_mixed(const void *x, int M, const void *w_fp4, const void *w_fp4_sc
   RDQ_REQUIRE(x != nullptr && y != nullptr, RDQ_E_INVALID, "x and y must not be null");
   RDQ_REQUIRE(aligned16(x) && aligned16(y), RDQ_E_INVALID, "x and y must be 16-byte aligned");
   RDQ_REQUIRE(K % 64 == 0, RDQ_E_UNSUPPORTED, "rdq_gemm_mixed needs K to be a multiple of 64, got K=%d", K);
+  // the kernel addresses each weight tensor with 32-bit byte offsets
+  RDQ_REQUIRE(1ll * n_fp4 * (K / 2) < (1ll << 32) && 1ll * n_fp8 * K < (1ll << 32) && 2ll * n_fp16 * K < (1ll << 32),
+              RDQ_E_UNSUPPORTED, "rdq_gemm_mixed: a format group of this layer exceeds 4 GB");
   GemmArgs a;
   a.x = static_cast<const __half *>(x);
   a.M = M;

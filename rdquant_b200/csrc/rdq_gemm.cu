@@ -2,30 +2,39 @@
 // sm_100a: dequantise-to-shared-memory producers feeding tcgen05 kind::f16 MMAs with the
 // FP32 accumulator in tensor memory.
 //
-// Tile: 128 tokens x 128 output channels per CTA, k blocks of 64.  The output tile is taken
-// in ORIGINAL channel order: channel n0 + j reads permuted row inv_perm[n0 + j], so the
-// permutation costs nothing on the store side (rows of all three formats meet in one tile).
+// Tile: 128 or 256 tokens x 128 or 256 output channels per CTA (the largest that still gives
+// every SM a CTA), k blocks of 64.  The output tile is taken in ORIGINAL channel order:
+// channel n0 + j reads permuted row inv_perm[n0 + j], so the permutation costs nothing on the
+// store side (rows of all three formats meet in one tile).
 //
 //   warp 0 (1 thread)   TMA (cp.async.bulk.tensor.2d, 128B swizzle) loads of the 128 x 64
-//                       activation block into the A stage.
-//   warp 1 (1 thread)   issues 4 x tcgen05.mma (M128 N128 K16) per k block, commits the
-//                       stage back to the producers, finally commits the accumulator.
-//                       The warp also owns the tensor-memory allocation.
-//   warps 2..8          224 dequantisation threads.  The 128 rows of the tile are sorted by
-//                       format and each format group is padded to whole warps, so every
-//                       warp runs one format's loop without divergence.  A thread owns one
-//                       weight row: it prefetches the next k block's packed bytes into
-//                       registers, converts the current one to f16 (NVFP4: hardware E2M1
-//                       converter times the block scale, exact in f16; FP8: E4M3 converter,
-//                       channel scale deferred to the epilogue; FP16: copy) and stores the
-//                       64 halves as eight 16-byte chunks in the K-major 128B-swizzled
-//                       layout the MMA descriptor expects.
-//   epilogue (warps 2-5) tcgen05.ld of the accumulator (one token row per thread), channel
-//                       scale and bias, f16 conversion, 64-byte vector stores.
+//                       activation blocks into the A stage (one per 128 tokens).
+//   warp 1 (1 thread)   issues 4 x tcgen05.mma (M128, N = tile width, K16) per k block and
+//                       128-token accumulator, commits the stage back to the producers,
+//                       finally commits the accumulators.  The warp also owns the
+//                       tensor-memory allocation (up to all 512 columns).
+//   warps 2..           12 or 14 dequantisation warps.  The rows of the tile are sorted by
+//                       format and padded to groups of four; a warp takes every W-th group,
+//                       a quarter warp one row, a lane one 16-byte chunk (8 k) of it: it
+//                       loads the next k block's 4 / 8 / 16 packed bytes into registers,
+//                       converts the current ones to f16 (NVFP4: hardware E2M1 converter
+//                       times the block scale, exact in f16; FP8: E4M3 converter, channel
+//                       scale deferred to the epilogue; FP16: copy) and stores its chunk in
+//                       the K-major 128B-swizzled layout the MMA descriptor expects -- the
+//                       eight lanes of a row write 128 contiguous bytes (no bank conflicts)
+//                       and read 32 / 64 / 128 contiguous bytes.
+//   epilogue            twelve of those warps: tcgen05.ld of the accumulators (a warp reads
+//                       the 32 tensor-memory lanes of its quarter, the warps of a quarter
+//                       take the 32-column chunks in turn), channel scale and bias, f16
+//                       conversion, 64-byte vector stores.
 //
-// Shared memory: 4 stages x (16 KB A + 16 KB B).  All mbarrier waits are bounded; a wait
-// that runs out raises an abort flag that every role checks, and the kernel drains and
-// frees its tensor memory.
+// Shared memory: 4 stages x (16 or 32 KB A + 16 KB B), or 3 x (32 KB A + 32 KB B) for the
+// 256 x 256 tile.  All mbarrier waits are bounded; a wait that runs out raises an abort flag
+// that every role checks, and the kernel drains and frees its tensor memory.
+//
+// Measured on B200 (in-kernel clocks, 256 x 256 tile): with the weight conversion switched
+// off the pipeline runs at the MMA rate (1024 cycles per k block); with it, 1450 cycles --
+// the conversion warps' instruction issue is the bound, not L2 or shared-memory bandwidth.
 //
 // FLOPs per launch: 2*M*N*K.  Bound: dense f16 tensor throughput.
 //
@@ -61,6 +70,10 @@ struct GemmCfg {
   static constexpr int kSmem = kStages * (kStageAll + kStageB) + 1024;
   static constexpr int kMaxQuads = BN / 4 + 3;  // each format padded to a multiple of four rows
   static constexpr int kTasks = (kMaxQuads + kProducerWarps - 1) / kProducerWarps;
+#ifndef RDQ_GEMM_PF
+#define RDQ_GEMM_PF 1
+#endif
+  static constexpr int kPrefetch = RDQ_GEMM_PF;  // k blocks of packed weights held in registers ahead of use
 };
 
 struct GemmSmem {

@@ -52,23 +52,22 @@ __device__ __forceinline__ uint2 ldg_nc8(const void *p) {
   return v;
 }
 
-template <int NS, int SB, int TMAX>
+template <int NS, int SB, int TMAX, int PF>
 __device__ __forceinline__ void produce_rows(GemmSmem &S, const GemmArgs &a, uint32_t b_base, int pwarp, int nwarps,
                                              int lane, int nkb) {
   const int chunk = lane & 7, sub = lane >> 3;
   const int nq = S.nquad;
-  // per task: packed-byte pointer (already at this lane's chunk), scale pointer (NVFP4), row
-  // offset inside a stage, swizzle key, format (3 = write zeros, 4 = nothing to do)
-  const uint8_t *wp[TMAX];
-  const uint8_t *sp[TMAX];
-  uint32_t roff[TMAX];
+  // per task: 32-bit byte offset of this lane's chunk from the format's weight tensor (the
+  // launcher checks that the tensors are below 4 GB), offset of its block scale (NVFP4), row
+  // offset inside a stage (swizzle applied), format (3 = write zeros, 4 = nothing to do)
+  uint32_t woff[TMAX], soff[TMAX], roff[TMAX];
   int fmt[TMAX];
 #pragma unroll
   for (int t = 0; t < TMAX; ++t) {
     const int quad = pwarp + t * nwarps;
     fmt[t] = 4;
-    wp[t] = nullptr;
-    sp[t] = nullptr;
+    woff[t] = 0;
+    soff[t] = 0;
     roff[t] = 0;
     if (quad < nq) {
       const int j = S.prow[quad * 4 + sub];
@@ -79,70 +78,81 @@ __device__ __forceinline__ void produce_rows(GemmSmem &S, const GemmArgs &a, uin
           fmt[t] = 3;
         } else if (r < a.n4) {
           fmt[t] = 0;
-          wp[t] = a.w4 + 1ll * r * (a.K >> 1) + chunk * 4;
-          sp[t] = a.s4 + 1ll * r * (a.K >> 4) + (chunk >> 1);
+          woff[t] = static_cast<uint32_t>(r) * (a.K >> 1) + chunk * 4;
+          soff[t] = static_cast<uint32_t>(r) * (a.K >> 4) + (chunk >> 1);
         } else if (r < a.n4 + a.n8) {
           fmt[t] = 1;
-          wp[t] = a.w8 + 1ll * (r - a.n4) * a.K + chunk * 8;
+          woff[t] = static_cast<uint32_t>(r - a.n4) * a.K + chunk * 8;
         } else {
           fmt[t] = 2;
-          wp[t] = reinterpret_cast<const uint8_t *>(a.w16 + 1ll * (r - a.n4 - a.n8) * a.K) + chunk * 16;
+          woff[t] = static_cast<uint32_t>(r - a.n4 - a.n8) * (a.K * 2) + chunk * 16;
         }
       }
     }
   }
+  const uint8_t *w16b = reinterpret_cast<const uint8_t *>(a.w16);
   auto load = [&](int t, int kb) {
     uint4 d = make_uint4(0u, 0u, 0u, 0u);
     if (fmt[t] == 0) {
-      d.x = ldg_nc4(wp[t] + kb * 32);
-      d.y = ldg_nc1(sp[t] + kb * 4);
+      d.x = ldg_nc4(a.w4 + (woff[t] + kb * 32u));
+      d.y = ldg_nc1(a.s4 + (soff[t] + kb * 4u));
     } else if (fmt[t] == 1) {
-      const uint2 v = ldg_nc8(wp[t] + kb * 64);
+      const uint2 v = ldg_nc8(a.w8 + (woff[t] + kb * 64u));
       d.x = v.x;
       d.y = v.y;
     } else if (fmt[t] == 2) {
-      d = ldg_nc16(wp[t] + kb * 128);
+      d = ldg_nc16(w16b + (woff[t] + kb * 128u));
     }
     return d;
   };
   StageCursor<NS> cur;
-  uint4 q[TMAX];
+  // packed bytes of the next PF k blocks sit in registers: a load is issued PF blocks before
+  // its use (L2 latency under load is longer than one k block's MMA time)
+  uint4 q[PF][TMAX];
 #pragma unroll
-  for (int t = 0; t < TMAX; ++t) q[t] = load(t, 0);
-  for (int kb = 0; kb < nkb; ++kb) {
-    uint4 c[TMAX];
+  for (int p = 0; p < PF; ++p) {
 #pragma unroll
-    for (int t = 0; t < TMAX; ++t) c[t] = q[t];
-    if (kb + 1 < nkb) {
+    for (int t = 0; t < TMAX; ++t) q[p][t] = (p < nkb) ? load(t, p) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  for (int kbase = 0; kbase < nkb; kbase += PF) {
 #pragma unroll
-      for (int t = 0; t < TMAX; ++t) q[t] = load(t, kb + 1);
-    }
-    if (threadIdx.x == 64) GTL(kb, 3);
-    cur.begin(S);
-    if (threadIdx.x == 64) GTL(kb, 4);
-    const uint32_t sbase = b_base + cur.s * SB;
+    for (int p = 0; p < PF; ++p) {
+      const int kb = kbase + p;
+      if (kb >= nkb) break;
+      uint4 c[TMAX];
 #pragma unroll
-    for (int t = 0; t < TMAX; ++t) {
-      uint32_t o0 = 0u, o1 = 0u, o2 = 0u, o3 = 0u;
-      if (fmt[t] == 0) {
-        const uint32_t scl = __byte_perm(cvt_e4m3x2(c[t].y), 0u, 0x1010u);
-        cvt_e2m1x8(c[t].x, o0, o1, o2, o3);
-        o0 = hmul2_u32(o0, scl);
-        o1 = hmul2_u32(o1, scl);
-        o2 = hmul2_u32(o2, scl);
-        o3 = hmul2_u32(o3, scl);
-      } else if (fmt[t] == 1) {
-        cvt_e4m3x4(c[t].x, o0, o1);
-        cvt_e4m3x4(c[t].y, o2, o3);
-      } else if (fmt[t] == 2) {
-        o0 = c[t].x; o1 = c[t].y; o2 = c[t].z; o3 = c[t].w;
+      for (int t = 0; t < TMAX; ++t) c[t] = q[p][t];
+      if (kb + PF < nkb) {
+#pragma unroll
+        for (int t = 0; t < TMAX; ++t) q[p][t] = load(t, kb + PF);
       }
-      if (fmt[t] != 4)
-        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sbase + roff[t]), "r"(o0), "r"(o1), "r"(o2), "r"(o3)
-                     : "memory");
+      if (threadIdx.x == 64) GTL(kb, 3);
+      cur.begin(S);
+      if (threadIdx.x == 64) GTL(kb, 4);
+      const uint32_t sbase = b_base + cur.s * SB;
+#pragma unroll
+      for (int t = 0; t < TMAX; ++t) {
+        uint32_t o0 = 0u, o1 = 0u, o2 = 0u, o3 = 0u;
+        if (fmt[t] == 0) {
+          const uint32_t scl = __byte_perm(cvt_e4m3x2(c[t].y), 0u, 0x1010u);
+          cvt_e2m1x8(c[t].x, o0, o1, o2, o3);
+          o0 = hmul2_u32(o0, scl);
+          o1 = hmul2_u32(o1, scl);
+          o2 = hmul2_u32(o2, scl);
+          o3 = hmul2_u32(o3, scl);
+        } else if (fmt[t] == 1) {
+          cvt_e4m3x4(c[t].x, o0, o1);
+          cvt_e4m3x4(c[t].y, o2, o3);
+        } else if (fmt[t] == 2) {
+          o0 = c[t].x; o1 = c[t].y; o2 = c[t].z; o3 = c[t].w;
+        }
+        if (fmt[t] != 4)
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sbase + roff[t]), "r"(o0), "r"(o1), "r"(o2), "r"(o3)
+                       : "memory");
+      }
+      cur.end(S);
+      if (threadIdx.x == 64) GTL(kb, 5);
     }
-    cur.end(S);
-    if (threadIdx.x == 64) GTL(kb, 5);
   }
 }
 
@@ -269,7 +279,7 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------- weight dequantisation
-    produce_rows<NS, SB, Cfg::kTasks>(S, a, b_base, warp - 2, Cfg::kProducerWarps, lane, nkb);
+    produce_rows<NS, SB, Cfg::kTasks, Cfg::kPrefetch>(S, a, b_base, warp - 2, Cfg::kProducerWarps, lane, nkb);
 
     // ----------------------------------------------------------------------- epilogue
     // A warp may read the tensor-memory lanes 32 (warp % 4) ...; the producer warps that share a
