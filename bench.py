@@ -145,6 +145,7 @@ def cpu_baseline(budget_s: float = 12.0) -> dict:
     from rdquant_b200.synthetic import QWEN3_4B_BLOCK, fixed_splits, synthetic_weight
 
     oracle_c.build()
+    oracle_c.set_threads(os.cpu_count() or 1)  # launchers like torchrun export OMP_NUM_THREADS=1
     k, n = QWEN3_4B_BLOCK["gate_proj"]
     gen = torch.Generator().manual_seed(4)
     w = synthetic_weight(n, k, gen)

@@ -31,6 +31,14 @@ def lib():
     return _lib
 
 
+def set_threads(n: int) -> None:
+    """Use n OpenMP threads (torchrun exports OMP_NUM_THREADS=1; the timed baseline wants all cores)."""
+    l = lib()
+    l.rdq_oracle_set_threads.argtypes = [ctypes.c_int]
+    l.rdq_oracle_set_threads.restype = None
+    l.rdq_oracle_set_threads(int(n))
+
+
 def threads() -> int:
     return int(lib().rdq_oracle_threads())
 

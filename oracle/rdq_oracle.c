@@ -18,6 +18,16 @@
 static const float kLut[16] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f,
                                -0.0f, -0.5f, -1.0f, -1.5f, -2.0f, -3.0f, -4.0f, -6.0f};
 
+/* Use `n` OpenMP threads from now on (launchers such as torchrun export OMP_NUM_THREADS=1;
+ * the timed CPU baseline wants all host cores).  n <= 0 leaves the setting alone. */
+void rdq_oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int rdq_oracle_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();
