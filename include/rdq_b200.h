@@ -197,6 +197,28 @@ int rdq_gemm_mixed(const void *x, int M,
                    int n_fp4, int n_fp8, int n_fp16, int K,
                    void *stream);
 
+/*
+ * Encoders: one format group of a float weight matrix -> its packed checkpoint
+ * tensors, bit for bit what the reference's CPU encoders and checkpoint writer
+ * produce (rdquant/core/formats.py:84-142 nvfp4_quantize, :166-193
+ * fp8_quantize; rdquant/integrations/hf_export.py:81-102), plus what the
+ * per-channel MSE of the format search needs (rdquant/core/formats.py:414-436
+ * compute_mse_2d): row_sqerr[i] = sum_k (w[i,k] - dequant(quant(w))[i,k])^2.
+ *   w        f32 (w_is_f32 != 0) or f16 [n, K], 16-byte aligned, K % 16 == 0
+ *   NVFP4:   codes u8 [n, K/2], scales u8 [n, K/16] (E4M3 bits);
+ *            max_scale (1 float, may be NULL) receives the largest block scale
+ *            (the reference's global_scale metadata; 0 if all blocks are 0)
+ *   FP8:     out u8 [n, K]; scale_out f32 [n] (may be NULL) receives the group's
+ *            one scale = absmax / 448 in every entry; absmax_scratch: 1 float
+ *   row_sqerr f32 [n] or NULL.
+ */
+int rdq_quantize_nvfp4(const void *w, int w_is_f32, int n, int K,
+                       void *codes, void *scales, float *row_sqerr,
+                       float *max_scale, void *stream);
+int rdq_quantize_fp8(const void *w, int w_is_f32, int n, int K,
+                     void *out, float *scale_out, float *row_sqerr,
+                     float *absmax_scratch, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

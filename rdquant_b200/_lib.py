@@ -21,6 +21,7 @@ SOURCES = [
     "rdq_gemv_stream.cu",
     "rdq_gemv_tiled.cu",
     "rdq_gemm.cu",
+    "rdq_quantize.cu",
 ]
 HEADERS = ["rdq_common.cuh", "rdq_kernels.cuh", "rdq_gemv_tiled_kernel.inl", "rdq_gemv_tiled_kernel2.inl", "rdq_gemm_kernel.inl",
            os.path.join("..", "..", "include", "rdq_b200.h")]
@@ -90,6 +91,10 @@ def _bind(lib: ctypes.CDLL) -> None:
     lib.rdq_gemv_tiled_noalloc.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, i32, i32, i32, i32, i32, vp]
     lib.rdq_gemm_mixed.restype = i32
     lib.rdq_gemm_mixed.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
+    lib.rdq_quantize_nvfp4.restype = i32
+    lib.rdq_quantize_nvfp4.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp]
+    lib.rdq_quantize_fp8.restype = i32
+    lib.rdq_quantize_fp8.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp]
 
 
 EXPORTS = [
@@ -103,6 +108,8 @@ EXPORTS = [
     "rdq_gemv_tiled",
     "rdq_gemv_tiled_noalloc",
     "rdq_gemm_mixed",
+    "rdq_quantize_nvfp4",
+    "rdq_quantize_fp8",
 ]
 
 

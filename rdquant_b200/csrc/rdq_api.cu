@@ -238,4 +238,25 @@ int rdq_gemm_mixed(const void *x, int M, const void *w_fp4, const void *w_fp4_sc
   return launch_gemm(a, static_cast<cudaStream_t>(stream));
 }
 
+int rdq_quantize_nvfp4(const void *w, int w_is_f32, int n, int K, void *codes, void *scales, float *row_sqerr,
+                       float *max_scale, void *stream) {
+  RDQ_REQUIRE(n >= 0 && K > 0 && K % 16 == 0, RDQ_E_INVALID, "rdq_quantize_nvfp4 needs n >= 0 and K a positive multiple of 16 (n=%d K=%d)", n, K);
+  if (n == 0) return RDQ_OK;
+  RDQ_REQUIRE(w != nullptr && codes != nullptr && scales != nullptr, RDQ_E_INVALID, "w, codes and scales must not be null");
+  RDQ_REQUIRE(aligned16(w) && (reinterpret_cast<uintptr_t>(codes) & 7) == 0, RDQ_E_INVALID,
+              "w must be 16-byte aligned and codes 8-byte aligned");
+  return launch_quantize_nvfp4(w, w_is_f32 != 0, n, K, static_cast<uint8_t *>(codes), static_cast<uint8_t *>(scales), row_sqerr,
+                               max_scale, static_cast<cudaStream_t>(stream));
+}
+
+int rdq_quantize_fp8(const void *w, int w_is_f32, int n, int K, void *out, float *scale_out, float *row_sqerr,
+                     float *absmax_scratch, void *stream) {
+  RDQ_REQUIRE(n >= 0 && K > 0 && K % 16 == 0, RDQ_E_INVALID, "rdq_quantize_fp8 needs n >= 0 and K a positive multiple of 16 (n=%d K=%d)", n, K);
+  if (n == 0) return RDQ_OK;
+  RDQ_REQUIRE(w != nullptr && out != nullptr && absmax_scratch != nullptr, RDQ_E_INVALID, "w, out and absmax_scratch must not be null");
+  RDQ_REQUIRE(aligned16(w) && aligned16(out), RDQ_E_INVALID, "w and out must be 16-byte aligned");
+  return launch_quantize_fp8(w, w_is_f32 != 0, n, K, static_cast<uint8_t *>(out), scale_out, row_sqerr, absmax_scratch,
+                             static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

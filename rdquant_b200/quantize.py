@@ -101,6 +101,52 @@ def quantize_weight(weight: torch.Tensor, permutation: torch.Tensor, splits: dic
     )
 
 
+def quantize_weight_packed(weight: torch.Tensor, permutation: torch.Tensor, splits: dict, bias=None) -> dict:
+    """GPU fast path of ``pack_layer(quantize_weight(...))``: the checkpoint tensors of one layer
+    straight from a CUDA weight ``[N, K]`` (K % 16 == 0), encoded by the CUDA encoders.
+
+    Byte-identical to the host route (rdquant/quantize.py:233-280 followed by
+    rdquant/integrations/hf_export.py:58-125); tensors stay on the weight's device.
+    """
+    from rdquant_b200 import rdquant_cuda
+
+    if not weight.is_cuda:
+        raise RuntimeError("quantize_weight_packed runs on CUDA tensors only")
+    n_out, n_in = weight.shape
+    perm = permutation.to(device=weight.device, dtype=torch.long)
+    if sum(splits.get(f, 0) for f in FORMAT_ORDER) != n_out:
+        raise ValueError("splits must sum to the number of output channels")
+    grouped = weight[perm]
+    if grouped.dtype not in (torch.float16, torch.float32):
+        grouped = grouped.float()
+    out = {
+        "splits": torch.tensor([int(splits.get(f, 0)) for f in FORMAT_ORDER], dtype=torch.int32),
+        "inv_permutation": inverse_permutation(perm).to(torch.int32),
+    }
+    start = 0
+    for fmt in FORMAT_ORDER:
+        n = int(splits.get(fmt, 0))
+        if n == 0:
+            continue
+        rows = grouped[start:start + n]
+        if fmt == "NVFP4":
+            enc = rdquant_cuda.quantize_nvfp4_packed(rows)
+            out["weight_nvfp4"] = enc["weight_nvfp4"]
+            out["weight_nvfp4_scale"] = enc["weight_nvfp4_scale"]
+            top = enc["global_scale"]
+            out["nvfp4_global_scale"] = torch.where(top == 0, torch.ones_like(top), top)
+        elif fmt == "FP8":
+            enc = rdquant_cuda.quantize_fp8_packed(rows)
+            out["weight_fp8"] = enc["weight_fp8"]
+            out["weight_fp8_scale"] = enc["weight_fp8_scale"]
+        else:
+            out["weight_fp16"] = rows.float().to(torch.float16).to(torch.bfloat16)
+        start += n
+    if bias is not None:
+        out["bias"] = bias.detach().clone()
+    return out
+
+
 class QuantizedLayer(nn.Module):
     """``nn.Linear`` replacement holding a :class:`QuantizedWeight`
     (reference: rdquant/quantize.py:76-135)."""

@@ -249,3 +249,54 @@ def fused_mixed_gemv(x: torch.Tensor, w_fp4: torch.Tensor, w_fp4_scales: torch.T
         "n_fp4": int(N_fp4), "n_fp8": int(N_fp8), "n_fp16": 0, "k": int(K),
     }
     return mixed_gemv(x, fd)
+
+
+def quantize_nvfp4_packed(w: torch.Tensor, want_sqerr: bool = False) -> dict:
+    """Encode a CUDA weight group ``[n, K]`` (f16 or f32, K % 16 == 0) as NVFP4 on the GPU.
+
+    Returns the checkpoint tensors ``weight_nvfp4`` u8 [n, K/2] and ``weight_nvfp4_scale`` u8
+    [n, K/16], bit-identical to the reference encoder + writer (rdquant/core/formats.py:84-142,
+    rdquant/integrations/hf_export.py:81-92), ``global_scale`` (largest block scale, 1.0 if all
+    are zero) and, on request, ``row_sqerr`` f32 [n] = per-row sum of squared reconstruction errors.
+    """
+    _need_cuda("w", w)
+    if w.dim() != 2 or w.dtype not in (torch.float16, torch.float32):
+        raise RuntimeError("quantize_nvfp4_packed expects a 2-D float16 or float32 CUDA tensor")
+    w = w.contiguous()
+    n, k = w.shape
+    codes = torch.empty(n, k // 2, dtype=torch.uint8, device=w.device)
+    scales = torch.empty(n, max(k // 16, 0), dtype=torch.uint8, device=w.device)
+    sq = torch.empty(n, dtype=torch.float32, device=w.device) if want_sqerr else None
+    top = torch.zeros(1, dtype=torch.float32, device=w.device)
+    with _on_device(w.device):
+        _lib.check(_lib.lib().rdq_quantize_nvfp4(_ptr(w), int(w.dtype == torch.float32), n, k, _ptr(codes), _ptr(scales),
+                                                 _ptr(sq), _ptr(top), _stream(w.device)), "rdq_quantize_nvfp4")
+    out = {"weight_nvfp4": codes, "weight_nvfp4_scale": scales, "global_scale": top}
+    if want_sqerr:
+        out["row_sqerr"] = sq
+    return out
+
+
+def quantize_fp8_packed(w: torch.Tensor, want_sqerr: bool = False) -> dict:
+    """Encode a CUDA weight group ``[n, K]`` as FP8 (E4M3, one scale for the group) on the GPU.
+
+    Returns ``weight_fp8`` u8 [n, K] and ``weight_fp8_scale`` f32 [n] (the group scale repeated),
+    bit-identical to the reference (rdquant/core/formats.py:166-193,
+    rdquant/integrations/hf_export.py:99-110), and optionally ``row_sqerr``.
+    """
+    _need_cuda("w", w)
+    if w.dim() != 2 or w.dtype not in (torch.float16, torch.float32):
+        raise RuntimeError("quantize_fp8_packed expects a 2-D float16 or float32 CUDA tensor")
+    w = w.contiguous()
+    n, k = w.shape
+    out8 = torch.empty(n, k, dtype=torch.uint8, device=w.device)
+    sc = torch.empty(n, dtype=torch.float32, device=w.device)
+    sq = torch.empty(n, dtype=torch.float32, device=w.device) if want_sqerr else None
+    scratch = torch.zeros(1, dtype=torch.float32, device=w.device)
+    with _on_device(w.device):
+        _lib.check(_lib.lib().rdq_quantize_fp8(_ptr(w), int(w.dtype == torch.float32), n, k, _ptr(out8), _ptr(sc), _ptr(sq),
+                                               _ptr(scratch), _stream(w.device)), "rdq_quantize_fp8")
+    out = {"weight_fp8": out8, "weight_fp8_scale": sc}
+    if want_sqerr:
+        out["row_sqerr"] = sq
+    return out
