@@ -20,21 +20,9 @@ struct TSched {
     if (p < W) return e8 + static_cast<int>((p - w8) / u16);
     return e16;
   }
-  __device__ __forceinline__ long long pos_of_image(int s) const {
-    if (s < e4) return 1ll * s * u4;
-    if (s < e8) return w4 + 1ll * (s - e4) * u8;
-    return w8 + 1ll * (s - e8) * u16;
-  }
   __device__ __forceinline__ int boundary(int b) const {
     if (b >= G) return e16;
     return image_of_pos(W * b / G);
-  }
-  __device__ int cta_of_image(int s) const {
-    int b = static_cast<int>(pos_of_image(s) * G / W);
-    if (b >= G) b = G - 1;
-    while (b + 1 < G && boundary(b + 1) <= s) ++b;
-    while (b > 0 && boundary(b) > s) --b;
-    return b;
   }
   __device__ __forceinline__ int tile_of_image(int s) const {
     if (s < e4) return s / S4;
@@ -48,34 +36,6 @@ struct TSched {
   }
 };
 
-// The images of one 16-row tile that this CTA streams.
-struct TSeg {
-  int fmt;        // 0 NVFP4, 1 FP8, 2 FP16
-  int gtile;      // tile index over all groups
-  int first_img;  // first image of the tile (global numbering)
-  int S;          // images in the tile
-  int c0, c1;     // chunk range of this CTA
-  bool starts, ends;
-};
-
-__device__ __forceinline__ TSeg tseg_at(const TSched &sc, int s_begin, int s_end, int gtile) {
-  TSeg sg;
-  sg.gtile = gtile;
-  if (gtile < sc.t4) {
-    sg.fmt = 0; sg.S = sc.S4; sg.first_img = gtile * sc.S4;
-  } else if (gtile < sc.t4 + sc.t8) {
-    sg.fmt = 1; sg.S = sc.S8; sg.first_img = sc.e4 + (gtile - sc.t4) * sc.S8;
-  } else {
-    sg.fmt = 2; sg.S = sc.S16; sg.first_img = sc.e8 + (gtile - sc.t4 - sc.t8) * sc.S16;
-  }
-  const int a = max(s_begin, sg.first_img), b = min(s_end, sg.first_img + sg.S);
-  sg.c0 = a - sg.first_img;
-  sg.c1 = b - sg.first_img;
-  sg.starts = (sg.c0 == 0);
-  sg.ends = (sg.c1 == sg.S);
-  return sg;
-}
-
 // processing order of a CTA's tile segments: the (possibly split) first tile, whose
 // partial another CTA is waiting for, then the (possibly split) last tile, which this
 // CTA finishes, then the whole tiles in between
@@ -85,19 +45,6 @@ __device__ __forceinline__ int tseg_order(int q, int nseg) {
   return q - 1;
 }
 
-__device__ __forceinline__ void t_st_release(int32_t *p, int32_t v) {
-  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ int32_t t_ld_acquire(const int32_t *p) {
-  int32_t v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ float t_ld_cg(const float *p) {
-  float v;
-  asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-  return v;
-}
 // x is written by the preceding kernel: coherent loads, issued only after the PDL wait
 __device__ __forceinline__ uint4 t_ldx16(const __half *p) {
   uint4 v;
