@@ -407,7 +407,7 @@ def main() -> None:
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": sum(2 * m * l["k"] for l in layers),
                 "d2h_bytes_per_step": sum(2 * m * l["n"] for l in layers), "steps": e2e_steps,
                 "ms_per_step": 1e3 * te / e2e_steps,
-                "api": "inference.GraphedDecodeStep.run(): pinned host x -> device, fused GEMVs, y -> pinned host as one CUDA-graph replay, synchronised every step; weight copies rotate as in the device-only measurement"},
+                "api": "inference.GraphedDecodeStep.run(): pinned host x -> device (staging kernel reading the pinned buffer), fused GEMVs, y -> pinned host (staging kernel) as one CUDA-graph replay, synchronised every step; weight copies rotate as in the device-only measurement"},
         "clocks": clocks,
         "status_words_nonzero": status_bad,
     }

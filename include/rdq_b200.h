@@ -219,6 +219,18 @@ int rdq_quantize_fp8(const void *w, int w_is_f32, int n, int K,
                      void *out, float *scale_out, float *row_sqerr,
                      float *absmax_scratch, void *stream);
 
+/*
+ * Copy `bytes` bytes between device-accessible buffers with a small kernel
+ * rather than the copy engine: meant for the few KB of activations / results a
+ * decode step moves between pinned (mapped) host memory and device memory
+ * inside a CUDA graph, where a memcpy node costs ~10 us of fixed latency.
+ * dst and src 16-byte aligned; either may be pinned host memory (the host
+ * pointer is valid on the device under unified addressing).  No counterpart in
+ * the reference, whose end-to-end path keeps activations on the device
+ * (benchmarks/bench_e2e.py:103-155).
+ */
+int rdq_stage_copy(void *dst, const void *src, size_t bytes, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -22,6 +22,7 @@ SOURCES = [
     "rdq_gemv_tiled.cu",
     "rdq_gemm.cu",
     "rdq_quantize.cu",
+    "rdq_stage.cu",
 ]
 HEADERS = ["rdq_common.cuh", "rdq_kernels.cuh", "rdq_gemv_tiled_kernel.inl", "rdq_gemv_tiled_kernel2.inl", "rdq_gemm_kernel.inl",
            os.path.join("..", "..", "include", "rdq_b200.h")]
@@ -95,6 +96,8 @@ def _bind(lib: ctypes.CDLL) -> None:
     lib.rdq_quantize_nvfp4.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp]
     lib.rdq_quantize_fp8.restype = i32
     lib.rdq_quantize_fp8.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp]
+    lib.rdq_stage_copy.restype = i32
+    lib.rdq_stage_copy.argtypes = [vp, vp, ctypes.c_size_t, vp]
 
 
 EXPORTS = [
@@ -110,6 +113,7 @@ EXPORTS = [
     "rdq_gemm_mixed",
     "rdq_quantize_nvfp4",
     "rdq_quantize_fp8",
+    "rdq_stage_copy",
 ]
 
 

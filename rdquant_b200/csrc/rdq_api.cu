@@ -259,4 +259,10 @@ int rdq_quantize_fp8(const void *w, int w_is_f32, int n, int K, void *out, float
                              static_cast<cudaStream_t>(stream));
 }
 
+int rdq_stage_copy(void *dst, const void *src, size_t bytes, void *stream) {
+  RDQ_REQUIRE(bytes == 0 || (dst != nullptr && src != nullptr), RDQ_E_INVALID, "dst and src must not be null");
+  RDQ_REQUIRE(aligned16(dst) && aligned16(src), RDQ_E_INVALID, "dst and src must be 16-byte aligned");
+  return launch_stage_copy(dst, src, bytes, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -78,6 +78,9 @@ int gemv_tiled_noalloc(const GemvTiledArgs &a, bool pdl, cudaStream_t stream);
 
 int launch_gemm(const GemmArgs &a, cudaStream_t stream);
 
+// staging copy by kernel (rdq_stage.cu)
+int launch_stage_copy(void *dst, const void *src, size_t bytes, cudaStream_t stream);
+
 // encoders (rdq_quantize.cu)
 int launch_quantize_nvfp4(const void *w, bool w_is_f32, int n, int K, uint8_t *codes, uint8_t *scales, float *row_sqerr,
                           float *max_scale, cudaStream_t stream);

@@ -300,3 +300,20 @@ def quantize_fp8_packed(w: torch.Tensor, want_sqerr: bool = False) -> dict:
     if want_sqerr:
         out["row_sqerr"] = sq
     return out
+
+
+def stage_copy(dst: torch.Tensor, src: torch.Tensor) -> None:
+    """Copy ``src`` into ``dst`` (same byte size, contiguous) with a small kernel on the current
+    stream.  One side lives on the GPU, the other may be pinned host memory: inside a CUDA
+    graph this replaces a memcpy node and its fixed latency."""
+    dev_t = dst if dst.is_cuda else src
+    if not dev_t.is_cuda:
+        raise RuntimeError("stage_copy needs one CUDA tensor")
+    for t in (dst, src):
+        if not t.is_contiguous() or not (t.is_cuda or t.is_pinned()):
+            raise RuntimeError("stage_copy expects contiguous CUDA or pinned host tensors")
+    nbytes = dst.numel() * dst.element_size()
+    if nbytes != src.numel() * src.element_size():
+        raise RuntimeError("stage_copy: size mismatch")
+    with _on_device(dev_t.device):
+        _lib.check(_lib.lib().rdq_stage_copy(_ptr(dst), _ptr(src), nbytes, _stream(dev_t.device)), "rdq_stage_copy")
