@@ -197,7 +197,7 @@ def run_prefill(args, device, rank: int, world: int) -> None:
 
     m = args.prefill
     steps, warmup = max(min(args.steps, 50), 1), max(args.warmup, 3)
-    units = build_block(device, seed=rank, copies=1, fuse=False)
+    units = build_block(device, seed=rank, copies=1, fuse=not args.no_fuse)
     gen = torch.Generator().manual_seed(99 + rank)
     xs = [torch.randn(m, u["k"], generator=gen).half().to(device) for u in units]
     flops = sum(2.0 * m * u["n"] * u["k"] for u in units)
@@ -229,7 +229,8 @@ def run_prefill(args, device, rank: int, world: int) -> None:
         "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16xf16->f32", "data": "synthetic",
         "config": {"workload": f"qwen3-4b decoder block: 7 mixed-precision linears, prefill GEMM at M={m} tokens "
-                               "(BASELINE configs[2])", "l2_policy": "activations + outputs of a step exceed L2 for M >= 2048"},
+                               "(BASELINE configs[2])", "launches_per_step": len(units),
+                   "fusion": "q/k/v and gate/up packed as one layer each" if not args.no_fuse else "none", "l2_policy": "activations + outputs of a step exceed L2 for M >= 2048"},
         "gpu_launches": steps * len(units),
         "roofline": {"bound": "tensor", "achieved": tf, "peak": sustained, "unit": "TFLOP/s", "frac": tf / sustained,
                      "traffic": None, "peak_source": kind + " (sustained cuBLAS bf16)", "kernel": "gemm_mixed_kernel"},
