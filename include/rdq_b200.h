@@ -198,6 +198,27 @@ int rdq_gemm_mixed(const void *x, int M,
                    void *stream);
 
 /*
+ * The same GEMM with caller scratch.  Problems with few output tiles (small M
+ * or N) leave SMs idle; given `workspace` of at least the size
+ * rdq_gemm_workspace_size reports (FP32, up to 4 x M x N), up to four CTAs share
+ * the k range of a tile and a second kernel adds their sums, applies channel
+ * scale and bias and writes y.  With workspace NULL (or too small) it behaves
+ * like rdq_gemm_mixed.  Results may differ from the unsplit launch in the last
+ * bit of the FP32 sum (different summation order); they are deterministic.
+ * No counterpart in the reference (cuBLAS picks its own split there).
+ */
+int rdq_gemm_workspace_size(int M, int N, int K, size_t *bytes);
+int rdq_gemm_mixed_ws(const void *x, int M,
+                      const void *w_fp4, const void *w_fp4_scales,
+                      float w_fp4_global_scale,
+                      const void *w_fp8, const float *w_fp8_scales,
+                      const void *w_fp16,
+                      const int32_t *inv_perm, const void *bias,
+                      void *y,
+                      int n_fp4, int n_fp8, int n_fp16, int K,
+                      void *workspace, size_t workspace_bytes, void *stream);
+
+/*
  * Encoders: one format group of a float weight matrix -> its packed checkpoint
  * tensors, bit for bit what the reference's CPU encoders and checkpoint writer
  * produce (rdquant/core/formats.py:84-142 nvfp4_quantize, :166-193

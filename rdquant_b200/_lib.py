@@ -92,6 +92,10 @@ def _bind(lib: ctypes.CDLL) -> None:
     lib.rdq_gemv_tiled_noalloc.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, i32, i32, i32, i32, i32, vp]
     lib.rdq_gemm_mixed.restype = i32
     lib.rdq_gemm_mixed.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
+    lib.rdq_gemm_mixed_ws.restype = i32
+    lib.rdq_gemm_mixed_ws.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, ctypes.c_size_t, vp]
+    lib.rdq_gemm_workspace_size.restype = i32
+    lib.rdq_gemm_workspace_size.argtypes = [i32, i32, i32, ctypes.POINTER(ctypes.c_size_t)]
     lib.rdq_quantize_nvfp4.restype = i32
     lib.rdq_quantize_nvfp4.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp]
     lib.rdq_quantize_fp8.restype = i32
@@ -111,6 +115,8 @@ EXPORTS = [
     "rdq_gemv_tiled",
     "rdq_gemv_tiled_noalloc",
     "rdq_gemm_mixed",
+    "rdq_gemm_mixed_ws",
+    "rdq_gemm_workspace_size",
     "rdq_quantize_nvfp4",
     "rdq_quantize_fp8",
     "rdq_stage_copy",

@@ -205,10 +205,10 @@ int rdq_gemv_tiled_noalloc(const void *x, int M, const void *w_tiled, const floa
   return gemv_tiled_noalloc(a, (flags & RDQ_GEMV_PDL) != 0, static_cast<cudaStream_t>(stream));
 }
 
-int rdq_gemm_mixed(const void *x, int M, const void *w_fp4, const void *w_fp4_scales,
-                   float w_fp4_global_scale, const void *w_fp8, const float *w_fp8_scales,
-                   const void *w_fp16, const int32_t *inv_perm, const void *bias, void *y, int n_fp4,
-                   int n_fp8, int n_fp16, int K, void *stream) {
+int rdq_gemm_mixed_ws(const void *x, int M, const void *w_fp4, const void *w_fp4_scales,
+                      float w_fp4_global_scale, const void *w_fp8, const float *w_fp8_scales,
+                      const void *w_fp16, const int32_t *inv_perm, const void *bias, void *y, int n_fp4,
+                      int n_fp8, int n_fp16, int K, void *workspace, size_t workspace_bytes, void *stream) {
   int rc = check_layer(w_fp4, w_fp4_scales, w_fp8, w_fp8_scales, w_fp16, n_fp4, n_fp8, n_fp16, K);
   if (rc != RDQ_OK) return rc;
   RDQ_REQUIRE(M >= 0, RDQ_E_INVALID, "M must be non-negative");
@@ -235,7 +235,25 @@ int rdq_gemm_mixed(const void *x, int M, const void *w_fp4, const void *w_fp4_sc
   a.n8 = n_fp8;
   a.n16 = n_fp16;
   a.K = K;
-  return launch_gemm(a, static_cast<cudaStream_t>(stream));
+  a.ksplit = 1;
+  a.partial = nullptr;
+  RDQ_REQUIRE(workspace == nullptr || aligned16(workspace), RDQ_E_INVALID, "workspace must be 16-byte aligned");
+  return launch_gemm(a, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int rdq_gemm_mixed(const void *x, int M, const void *w_fp4, const void *w_fp4_scales,
+                   float w_fp4_global_scale, const void *w_fp8, const float *w_fp8_scales,
+                   const void *w_fp16, const int32_t *inv_perm, const void *bias, void *y, int n_fp4,
+                   int n_fp8, int n_fp16, int K, void *stream) {
+  return rdq_gemm_mixed_ws(x, M, w_fp4, w_fp4_scales, w_fp4_global_scale, w_fp8, w_fp8_scales, w_fp16, inv_perm, bias, y,
+                           n_fp4, n_fp8, n_fp16, K, nullptr, 0, stream);
+}
+
+int rdq_gemm_workspace_size(int M, int N, int K, size_t *bytes) {
+  RDQ_REQUIRE(bytes != nullptr, RDQ_E_INVALID, "bytes must not be null");
+  RDQ_REQUIRE(M >= 0 && N >= 0 && K > 0 && K % 64 == 0, RDQ_E_INVALID, "rdq_gemm_workspace_size: bad shape M=%d N=%d K=%d", M, N, K);
+  *bytes = (M == 0 || N == 0) ? 0 : gemm_workspace_bytes(M, N, K);
+  return RDQ_OK;
 }
 
 int rdq_quantize_nvfp4(const void *w, int w_is_f32, int n, int K, void *codes, void *scales, float *row_sqerr,

@@ -54,7 +54,7 @@ __device__ __forceinline__ uint2 ldg_nc8(const void *p) {
 
 template <int NS, int SB, int TMAX, int PF>
 __device__ __forceinline__ void produce_rows(GemmSmem &S, const GemmArgs &a, uint32_t b_base, int pwarp, int nwarps,
-                                             int lane, int nkb) {
+                                             int lane, int kb0, int nkb) {
   const int chunk = lane & 7, sub = lane >> 3;
   const int nq = S.nquad;
   // per task: 32-bit byte offset of this lane's chunk from the format's weight tensor (the
@@ -112,9 +112,9 @@ __device__ __forceinline__ void produce_rows(GemmSmem &S, const GemmArgs &a, uin
 #pragma unroll
   for (int p = 0; p < PF; ++p) {
 #pragma unroll
-    for (int t = 0; t < TMAX; ++t) q[p][t] = (p < nkb) ? load(t, p) : make_uint4(0u, 0u, 0u, 0u);
+    for (int t = 0; t < TMAX; ++t) q[p][t] = (kb0 + p < nkb) ? load(t, kb0 + p) : make_uint4(0u, 0u, 0u, 0u);
   }
-  for (int kbase = 0; kbase < nkb; kbase += PF) {
+  for (int kbase = kb0; kbase < nkb; kbase += PF) {
 #pragma unroll
     for (int p = 0; p < PF; ++p) {
       const int kb = kbase + p;
@@ -175,7 +175,10 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
   const int m0 = blockIdx.x * BM * MT;
   const int n0 = blockIdx.y * BN;
   const int N = a.n4 + a.n8 + a.n16;
-  const int nkb = a.K / BK;
+  // this CTA's k blocks [kb0, nkb): the whole K, or one of ksplit equal parts (blockIdx.z)
+  const int nkb_all = a.K / BK;
+  const int kb0 = static_cast<int>(1ll * blockIdx.z * nkb_all / a.ksplit);
+  const int nkb = static_cast<int>(1ll * (blockIdx.z + 1) * nkb_all / a.ksplit);
 
   if (tid == 0) {
     for (int i = 0; i < NS; ++i) {
@@ -236,7 +239,7 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
     if (lane == 0) {
       bool alive = true;
       int s = 0, ph = 0;
-      for (int kb = 0; kb < nkb && alive; ++kb) {
+      for (int kb = kb0; kb < nkb && alive; ++kb) {
         if (ph > 0) alive = gemm_wait(&S.empty[s], (ph - 1) & 1, &S.abort_flag);
         if (!alive) break;
         const uint32_t full = smem_u32(&S.full[s]);
@@ -257,7 +260,7 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
       constexpr uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
       bool alive = true;
       int s = 0, ph = 0;
-      for (int kb = 0; kb < nkb && alive; ++kb) {
+      for (int kb = kb0; kb < nkb && alive; ++kb) {
         GTL(kb, 0);
         alive = gemm_wait(&S.full[s], ph & 1, &S.abort_flag);
         if (!alive) break;
@@ -269,7 +272,7 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
           const uint64_t da = make_desc_sw128(a_base + s * kStageAll + mt * kStageA);
 #pragma unroll
           for (int k4 = 0; k4 < BK / 16; ++k4)
-            umma_f16(tmem + mt * BN, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0 ? 1u : 0u);
+            umma_f16(tmem + mt * BN, da + 2 * k4, db + 2 * k4, idesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
         }
         umma_commit(smem_u32(&S.empty[s]));
         GTL(kb, 2);
@@ -279,7 +282,7 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------- weight dequantisation
-    produce_rows<NS, SB, Cfg::kTasks, Cfg::kPrefetch>(S, a, b_base, warp - 2, Cfg::kProducerWarps, lane, nkb);
+    produce_rows<NS, SB, Cfg::kTasks, Cfg::kPrefetch>(S, a, b_base, warp - 2, Cfg::kProducerWarps, lane, kb0, nkb);
 
     // ----------------------------------------------------------------------- epilogue
     // A warp may read the tensor-memory lanes 32 (warp % 4) ...; the producer warps that share a
@@ -298,7 +301,19 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
           uint32_t r[32];
           tmem_ld32(tmem + (static_cast<uint32_t>(q * 32) << 16) + mt * BN + cc * 32, r);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          if (m < a.M) {
+          if (m < a.M && a.ksplit > 1) {
+            // split k range: raw FP32 sums go to this part's plane; scale, bias and the f16
+            // conversion happen in the reduction kernel
+            float *dst = a.partial + (1ll * blockIdx.z * a.M + m) * N + n0 + cc * 32;
+            if (n0 + cc * 32 + 32 <= N && (N & 3) == 0) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v)
+                *reinterpret_cast<uint4 *>(dst + 4 * v) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+            } else {
+              for (int e = 0; e < 32; ++e)
+                if (n0 + cc * 32 + e < N) dst[e] = __uint_as_float(r[e]);
+            }
+          } else if (m < a.M) {
             __half *dst = a.y + 1ll * m * N + n0 + cc * 32;
             if (n0 + cc * 32 + 32 <= N && (N & 7) == 0) {
 #pragma unroll
@@ -339,6 +354,20 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// y = f16(sum over parts * channel scale + bias) for a split launch
+__global__ void __launch_bounds__(256) gemm_reduce_kernel(const GemmArgs a, int N) {
+  const long long total = 1ll * a.M * N;
+  for (long long i = 1ll * blockIdx.x * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
+    const int n = static_cast<int>(i % N);
+    float v = 0.f;
+    for (int z = 0; z < a.ksplit; ++z) v += a.partial[z * total + i];
+    const int r = a.inv_perm ? a.inv_perm[n] : n;
+    const float scl = (r < a.n4) ? a.global4 : (r < a.n4 + a.n8 ? a.s8[r - a.n4] : 1.f);
+    const float bia = a.bias ? __half2float(a.bias[n]) : 0.f;
+    a.y[i] = __float2half_rn(fmaf(v, scl, bia));
+  }
+}
+
 template <int MT, int BN>
 int launch_cfg(const CUtensorMap &xmap, const GemmArgs &a, int N, cudaStream_t stream) {
   using Cfg = GemmCfg<MT, BN>;
@@ -349,12 +378,49 @@ int launch_cfg(const CUtensorMap &xmap, const GemmArgs &a, int N, cudaStream_t s
     RDQ_CUDA(cudaFuncSetAttribute(gemm_mixed_kernel<MT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
     attr_done[dev] = true;
   }
-  const dim3 grid((a.M + MT * BM - 1) / (MT * BM), (N + BN - 1) / BN);
+  const dim3 grid((a.M + MT * BM - 1) / (MT * BM), (N + BN - 1) / BN, a.ksplit);
   gemm_mixed_kernel<MT, BN><<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(xmap, a);
   RDQ_CUDA(cudaGetLastError());
+  if (a.ksplit > 1) {
+    long long blocks = (1ll * a.M * N + 255) / 256;
+    if (blocks > 8ll * sm_count()) blocks = 8ll * sm_count();
+    gemm_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(a, N);
+    RDQ_CUDA(cudaGetLastError());
+  }
   return RDQ_OK;
 }
 
+}  // namespace
+
+namespace {
+// Tile configuration (0: 128 x 128, 1: 256 tokens x 128, 2: 256 x 256) and k split of a problem.
+// Few tiles leave SMs idle for the whole launch: then up to four CTAs share a tile's k range
+// (as long as each keeps at least eight k blocks) and a second kernel adds their sums.
+struct GemmPlan {
+  int cfg, ksplit;
+};
+GemmPlan gemm_plan(int M, int N, int K) {
+  const int sms = sm_count();
+  const int t256 = (M + 255) / 256, t128 = (M + 127) / 128;
+  GemmPlan p{0, 1};
+  long long tiles;
+  if (1ll * t256 * ((N + 255) / 256) >= sms) {
+    p.cfg = 2;
+    tiles = 1ll * t256 * ((N + 255) / 256);
+  } else if (1ll * t256 * ((N + 127) / 128) >= sms) {
+    p.cfg = 1;
+    tiles = 1ll * t256 * ((N + 127) / 128);
+  } else {
+    p.cfg = 0;
+    tiles = 1ll * t128 * ((N + 127) / 128);
+  }
+  const int nkb = K / BK;
+  int split = static_cast<int>(sms / tiles);
+  if (split > 4) split = 4;
+  if (split > nkb / 8) split = nkb / 8;
+  if (split > 1) p.ksplit = split;
+  return p;
+}
 }  // namespace
 
 #ifdef RDQ_GEMM_TIMELINE
@@ -363,7 +429,7 @@ extern "C" int rdq_debug_gemm_timeline(long long *host_out) {
 }
 #endif
 
-int launch_gemm(const GemmArgs &a, cudaStream_t stream) {
+int launch_gemm(const GemmArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
   static EncodeTiledFn encode = nullptr;
   if (!encode) {
     cudaDriverEntryPointQueryResult qr;
@@ -383,12 +449,22 @@ int launch_gemm(const GemmArgs &a, cudaStream_t stream) {
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   RDQ_REQUIRE(rc == CUDA_SUCCESS, RDQ_E_CUDA, "cuTensorMapEncodeTiled failed with code %d", static_cast<int>(rc));
   // the largest tile that still gives every SM a CTA: 256 tokens x 256 channels, 256 x 128, 128 x 128
-  const int sms = sm_count();
-  const int t256 = (a.M + 255) / 256, t128 = (a.M + 127) / 128;
-  if (t256 * ((N + 255) / 256) >= sms) return launch_cfg<2, 256>(xmap, a, N, stream);
-  if (t256 * ((N + 127) / 128) >= sms) return launch_cfg<2, 128>(xmap, a, N, stream);
-  (void)t128;
-  return launch_cfg<1, 128>(xmap, a, N, stream);
+  GemmArgs b = a;
+  const GemmPlan plan = gemm_plan(a.M, N, a.K);
+  b.ksplit = 1;
+  b.partial = nullptr;
+  if (plan.ksplit > 1 && workspace != nullptr && workspace_bytes >= sizeof(float) * plan.ksplit * a.M * N) {
+    b.ksplit = plan.ksplit;
+    b.partial = static_cast<float *>(workspace);
+  }
+  if (plan.cfg == 2) return launch_cfg<2, 256>(xmap, b, N, stream);
+  if (plan.cfg == 1) return launch_cfg<2, 128>(xmap, b, N, stream);
+  return launch_cfg<1, 128>(xmap, b, N, stream);
+}
+
+size_t gemm_workspace_bytes(int M, int N, int K) {
+  const GemmPlan plan = gemm_plan(M, N, K);
+  return plan.ksplit > 1 ? sizeof(float) * plan.ksplit * M * N : 0;
 }
 
 }  // namespace rdq

@@ -37,6 +37,8 @@ struct GemmArgs {
   const __half *bias;
   __half *y;
   int n4, n8, n16, K;
+  int ksplit;      // CTAs that share the k range of a tile (blockIdx.z); 1 = no split
+  float *partial;  // ksplit > 1: raw FP32 sums [ksplit][M][N], reduced by a second kernel
 };
 
 int launch_dequant(const void *w_fp4, const void *w_fp4_scales, float global4, const void *w_fp8,
@@ -76,7 +78,8 @@ int launch_gemv_tiled(const GemvTiledArgs &a, bool pdl, cudaStream_t stream);
 // same kernel with the scratch in a library-owned device array (no allocation anywhere)
 int gemv_tiled_noalloc(const GemvTiledArgs &a, bool pdl, cudaStream_t stream);
 
-int launch_gemm(const GemmArgs &a, cudaStream_t stream);
+int launch_gemm(const GemmArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+size_t gemm_workspace_bytes(int M, int N, int K);
 
 // staging copy by kernel (rdq_stage.cu)
 int launch_stage_copy(void *dst, const void *src, size_t bytes, cudaStream_t stream);

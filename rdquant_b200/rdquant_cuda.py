@@ -181,6 +181,9 @@ def mixed_gemv(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None, f
     return y
 
 
+_gemm_ws: dict = {}  # device -> scratch tensor of the split-k GEMM
+
+
 def mixed_gemm(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Prefill GEMM ``y[M, N] = x[M, K] @ W.T (+ bias)`` on the tcgen05 path."""
     _need_cuda("x", x, torch.float16)
@@ -194,11 +197,23 @@ def mixed_gemm(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None) -
     if bias is not None:
         _need_cuda("bias", bias, torch.float16)
     y = torch.empty(m, n, dtype=torch.float16, device=x.device)
+    if m == 0 or n == 0:
+        return y
     with _on_device(x.device):
-        rc = _lib.lib().rdq_gemm_mixed(
+        # scratch for problems with few tiles (the library then splits the k range); the
+        # per-device buffer only grows and is reused by later calls on the same stream order
+        need = ctypes.c_size_t(0)
+        _lib.check(_lib.lib().rdq_gemm_workspace_size(m, n, k, ctypes.byref(need)), "rdq_gemm_workspace_size")
+        ws = None
+        if need.value:
+            ws = _gemm_ws.get(x.device)
+            if ws is None or ws.numel() < need.value:
+                ws = torch.empty(need.value, dtype=torch.uint8, device=x.device)
+                _gemm_ws[x.device] = ws
+        rc = _lib.lib().rdq_gemm_mixed_ws(
             _ptr(x), m, _ptr(fd.get("w_fp4_q")), _ptr(fd.get("w_fp4_scales")), float(fd.get("w_fp4_global_scale", 1.0)),
             _ptr(fd.get("w_fp8_q")), _ptr(fd.get("w_fp8_scales")), _ptr(fd.get("w_fp16")), _ptr(fd.get("inv_perm")),
-            _ptr(bias), _ptr(y), n4, n8, n16, k, _stream(x.device))
+            _ptr(bias), _ptr(y), n4, n8, n16, k, _ptr(ws), need.value, _stream(x.device))
     _lib.check(rc, "rdq_gemm_mixed")
     return y
 
