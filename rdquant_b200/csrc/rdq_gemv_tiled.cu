@@ -11,8 +11,8 @@
 // of 16 B, so ldmatrix reads of 8 rows never collide on a bank.
 //
 // Kernel: images are numbered in storage order and each CTA takes a contiguous,
-// cost-balanced range of them (an NVFP4 image costs more instructions than an FP8 or FP16
-// image of the same size).  Inside a CTA
+// time-balanced range of them (a small model of ring-resident and streamed images per format,
+// see launch_gemv_tiled).  Inside a CTA
 //   producer warp   writes the CTA's stage list (one word per image: format, chunk, "hand
 //                   over after this stage"), then one thread issues one cp.async.bulk
 //                   (TMA) copy per image (10-19 KB) into a shared-memory ring, mbarrier

@@ -3,12 +3,6 @@ namespace rdq {
 
 namespace {
 
-// scheduling cost of one NVFP4 / FP8 / FP16 image (build-time tunables)
-#ifndef RDQ_COST_U4
-#define RDQ_COST_U4 10
-#define RDQ_COST_U8 7
-#define RDQ_COST_U16 6
-#endif
 #ifndef RDQ_STAGE_UNROLL
 #define RDQ_STAGE_UNROLL 2
 #endif
@@ -671,31 +665,8 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
   sc.e4 = sc.t4 * sc.S4;
   sc.e8 = sc.e4 + sc.t8 * sc.S8;
   sc.e16 = sc.e8 + t16 * sc.S16;
-  // Images are balanced by what they cost an SM, not by their bytes: the kernel is bound by
-  // instruction issue, and a 16 x ck NVFP4 image (conversion + block scaling) costs more
-  // than an FP8 or FP16 image of the same size (weights chosen by measurement).
-  sc.u4 = RDQ_COST_U4;
-  sc.u8 = RDQ_COST_U8;
-  sc.u16 = RDQ_COST_U16;
   sc.img4 = img_bytes(0, ck);
   sc.img8 = img_bytes(1, ck);
-  sc.w4 = 1ll * sc.e4 * sc.u4;
-  sc.w8 = sc.w4 + 1ll * (sc.e8 - sc.e4) * sc.u8;
-  sc.W = sc.w8 + 1ll * (sc.e16 - sc.e8) * sc.u16;
-  // every CTA must own at least one image: its share may not be shorter than the
-  // heaviest image
-  int G = sm_count();
-  // ... and a tile may spread over at most 31 CTAs (the owner finds them with one ballot)
-  long long minshare = sc.u4;  // u4 is the largest cost
-  const long long tile_cost[3] = {1ll * sc.S4 * sc.u4, 1ll * sc.S8 * sc.u8, 1ll * sc.S16 * sc.u16};
-  for (int f = 0; f < 3; ++f)
-    if ((tile_cost[f] + 29) / 30 > minshare) minshare = (tile_cost[f] + 29) / 30;
-  const long long maxg = sc.W / minshare;
-  if (maxg < G) G = static_cast<int>(maxg);
-  if (G < 1) G = 1;
-  sc.G = G;
-  RDQ_REQUIRE(sc.W / G / sc.u16 + 2 <= kMaxList, RDQ_E_UNSUPPORTED,
-              "layer too large for the tiled GEMV: more than %d images per CTA", kMaxList);
 
   TiledArgs a;
   a.x = h.x; a.M = h.M; a.tiled = h.tiled; a.s8 = h.s8; a.global4 = h.global4; a.perm = h.perm;
@@ -732,6 +703,57 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
   if (nst < kGroups) nst = kGroups;  // 3 x 19 KB always fits beside the fixed part
   a.nstages = nst;
   const int smem = nst * a.slot_bytes + fixed + xbytes;
+
+  // Images are balanced by what they cost a CTA in time, not by their bytes: an NVFP4 image
+  // (conversion + block scaling) takes more instructions than an FP8 or FP16 image of the
+  // same size, but images beyond the ring's depth mostly cost the wait for their copy.
+  {
+    // Time model of a CTA that streams n images of one format (cycles, three warp groups):
+    // the first nst images are in the ring when the kernel may start and cost their compute
+    // time c; each later one costs (landing time + c) / slots per group.  Find the common
+    // finishing time T at which the three formats' images fill exactly the grid, and weigh
+    // an image by 1 / n(T).
+    // Constants measured on B200 with in-kernel clocks (compute) and fitted on the benchmark
+    // block (landing time: 2500 .. 7000 give the same step time within 2 %, 1200 is 8 % slower).
+    const double kappa[3] = {0.123, 0.0715, 0.038};  // compute cycles per image byte and group
+    const double land = 4500.0;                      // cycles from copy issue to landing under load
+    const double img[3] = {double(sc.img4), double(sc.img8), double(sc.img8)};
+    const double cnt[3] = {double(sc.e4), double(sc.e8 - sc.e4), double(sc.e16 - sc.e8)};
+    const double spg = double(nst) / kGroups;
+    auto n_of = [&](int f, double T) {
+      const double c = kappa[f] * img[f], p = (land + c) / spg;
+      const double t_ring = nst * c / kGroups;
+      return T <= t_ring ? T * kGroups / c : nst + (T - t_ring) * kGroups / p;
+    };
+    double lo = 1.0, hi = 1e9;
+    for (int it = 0; it < 60; ++it) {
+      const double T = 0.5 * (lo + hi);
+      double ctas = 0;
+      for (int f = 0; f < 3; ++f) ctas += cnt[f] / n_of(f, T);
+      if (ctas > sm_count()) lo = T; else hi = T;
+    }
+    const double n4 = n_of(0, hi), n8 = n_of(1, hi), n16 = n_of(2, hi);
+    sc.u4 = 1000;
+    sc.u8 = max(1, min(1000, static_cast<int>(1000.0 * n4 / n8 + 0.5)));
+    sc.u16 = max(1, min(sc.u8, static_cast<int>(1000.0 * n4 / n16 + 0.5)));
+  }
+  sc.w4 = 1ll * sc.e4 * sc.u4;
+  sc.w8 = sc.w4 + 1ll * (sc.e8 - sc.e4) * sc.u8;
+  sc.W = sc.w8 + 1ll * (sc.e16 - sc.e8) * sc.u16;
+  // every CTA must own at least one image: its share may not be shorter than the
+  // heaviest image
+  int G = sm_count();
+  // ... and a tile may spread over at most 31 CTAs (the owner finds them with one ballot)
+  long long minshare = sc.u4;  // u4 is the largest cost
+  const long long tile_cost[3] = {1ll * sc.S4 * sc.u4, 1ll * sc.S8 * sc.u8, 1ll * sc.S16 * sc.u16};
+  for (int f = 0; f < 3; ++f)
+    if ((tile_cost[f] + 29) / 30 > minshare) minshare = (tile_cost[f] + 29) / 30;
+  const long long maxg = sc.W / minshare;
+  if (maxg < G) G = static_cast<int>(maxg);
+  if (G < 1) G = 1;
+  sc.G = G;
+  RDQ_REQUIRE(sc.W / G / sc.u16 + 2 <= kMaxList, RDQ_E_UNSUPPORTED,
+              "layer too large for the tiled GEMV: more than %d images per CTA", kMaxList);
 
   static int smem_set[64][4] = {};
   int dev = 0;
