@@ -63,13 +63,13 @@ constexpr int kThreads = (kMmaWarps + 1 + kEpiWarps) * 32;  // + producer warp +
 // 512 threads: the launch bounds ask for two CTAs (this layer's and the next one's) per SM,
 // i.e. 64 registers per thread
 constexpr int kFlushRing = 2;  // slots of a hand-over ring (one per warp group and epilogue warp)
-constexpr int kMetaSegs = 32;
+constexpr int kMetaSegs = 16;       // tiles per CTA whose output metadata is preloaded into shared memory
 constexpr int kMaxStages = 12;
 #ifndef RDQ_CHUNK_MAX
 #define RDQ_CHUNK_MAX 2048
 #endif
 constexpr int kChunkMax = RDQ_CHUNK_MAX;  // longest k chunk of an image, in NVFP4 elements
-constexpr int kMaxList = 512;       // images one CTA can stream (stage list entries)
+constexpr int kMaxList = 256;       // images one CTA can stream (stage list entries)
 
 // pitch of a block-scale row inside an NVFP4 image: payload rounded up to 16 B plus a
 // skew that makes the pitch an odd multiple of 16 B (conflict-free 8-row reads)

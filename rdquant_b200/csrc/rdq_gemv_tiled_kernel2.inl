@@ -188,7 +188,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
   // hand-over rings, one per (warp group, epilogue warp): kFlushRing slots of
   // [4 warps][16 rows][mp] partial sums; each ring has one writer group and one reader warp,
   // which both follow its barriers phase by phase
-  const int mp = (M + 3) & ~3;  // rows of four floats: the epilogue reads 16 B at a time
+  const int mp = (M <= 3) ? M : ((M + 3) & ~3);  // M > 3: rows of four floats, read 16 B at a time
+  const int vp = (M <= 4) ? 4 : 16;               // row pitch of an epilogue warp's staging tile
   const int nepi = a.nepi;      // epilogue warps in use (1..kEpiWarps)
   const int gslot_floats = kWarpsPerGroup * kTileRows * mp;
   float *flush = reinterpret_cast<float *>(smem + nst * a.slot_bytes);
@@ -198,7 +199,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
   uint32_t *list = reinterpret_cast<uint32_t *>(meta_bia + kMetaSegs * kTileRows);
   uint32_t *segtab = list + kMaxList;
   float *vstage = reinterpret_cast<float *>(segtab + kMaxList);  // per epilogue warp: [16 rows][16] finished sums of a tile
-  uint8_t *xsm = reinterpret_cast<uint8_t *>(vstage + kEpiWarps * kTileRows * 16);
+  uint8_t *xsm = reinterpret_cast<uint8_t *>(vstage + kEpiWarps * kTileRows * vp);
   const int xpitch = 2 * a.K + 16;  // activation row pitch in shared memory: skewed against bank conflicts
 
   // lane L holds the first image of CTA bx + L (one call site for the 64-bit divisions)
@@ -264,9 +265,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
         const int q = (idx == 0) ? 0 : (idx == nseg - 1 ? 1 : idx + 1);
         uint32_t e = static_cast<uint32_t>(fmt) | (static_cast<uint32_t>(s_begin + rel - f) << 3) |
                      (static_cast<uint32_t>(q % nepi) << 11) | (static_cast<uint32_t>(rel) << 13);
-        // the group that takes this stage (it % kGroups) hands its sums over after its last
-        // stage of the tile
-        if (it + kGroups >= nimg || sc.tile_of_image(s_begin + rel_of(it + kGroups)) != gt) e |= kEntFlush;
+        // the group that takes this stage hands its sums over after its last stage of the tile;
+        // its next stage sits three slots further, or in its first slot of the next round
+        const int sl = it % nst;
+        const int nxt = (sl + kGroups < nst) ? it + kGroups : it + (nst - sl) + sl % kGroups;
+        if (nxt >= nimg || sc.tile_of_image(s_begin + rel_of(nxt)) != gt) e |= kEntFlush;
         list[it] = e;
       }
       __syncwarp();
@@ -318,7 +321,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
     // order) belongs to warp q % nepi.
     const int ej = warp - kMmaWarps - 1;
     if (ej >= nepi) return;
-    float *vst = vstage + ej * kTileRows * 16;
+    float *vst = vstage + ej * kTileRows * vp;
     // output column, scale and bias of every row this CTA finishes: constants of the
     // layer, fetched up front so that finishing a tile needs no global round trip.  With
     // more than one epilogue warp the first builds the segment table and the others do this.
@@ -382,13 +385,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
           const int ia = max(s_begin, f), ib = min(s_end, f + S);
           const int nstage = ib - ia;
           const int it0 = (q == 0) ? 0 : (q == 1 ? n0 : n0 + nl + (f - (s_begin + n0)));
-          const int g0 = it0 % kGroups;
           e = static_cast<uint32_t>(idx) | (ia == f ? 1u << 9 : 0u) | (ib == f + S ? 1u << 10 : 0u);
+          // groups that take a stage of this tile: stage i sits in slot i % nst, group slot % 3
+          int mask = 0;
+          for (int i = 0; i < nstage && mask != (1 << kGroups) - 1; ++i) mask |= 1 << (((it0 + i) % nst) % kGroups);
 #pragma unroll
           for (int g = 0; g < kGroups; ++g) {
-            int d = g - g0;
-            if (d < 0) d += kGroups;
-            if (d < nstage) {
+            if ((mask >> g) & 1) {
               inc |= 1 << (10 * g);
               e |= 1u << (11 + g);
             }
@@ -470,23 +473,40 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
       }
       // Sum first and give the ring slots back at once: the barrier arrival is a release,
       // and behind a global store it would wait for that store to be acknowledged.
+      if (M <= 3) {
+        // up to three activation rows: scalar reads, lane = (row, m parity)
 #pragma unroll 1
-      for (int j = 0; j < nitem; ++j) {
-        const int m0 = ((lane >> 4) + 2 * j) * 4;
-        if (m0 < M) {
-          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int m = lane >> 4; m < M; m += 2) {
+          float v = 0.f;
 #pragma unroll
           for (int g = 0; g < kGroups; ++g) {
             if ((e >> (11 + g)) & 1) {
               const float *ring = flush + ((g * nepi + ej) * kFlushRing + ((e >> (14 + 2 * g)) & 1)) * gslot_floats;
 #pragma unroll
-              for (int w = 0; w < kWarpsPerGroup; ++w) {
-                const float4 p = *reinterpret_cast<const float4 *>(ring + (w * kTileRows + row) * mp + m0);
-                v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
-              }
+              for (int w = 0; w < kWarpsPerGroup; ++w) v += ring[(w * kTileRows + row) * mp + m];
             }
           }
-          *reinterpret_cast<float4 *>(vst + row * 16 + m0) = v;
+          vst[row * vp + m] = v;
+        }
+      } else {
+#pragma unroll 1
+        for (int j = 0; j < nitem; ++j) {
+          const int m0 = ((lane >> 4) + 2 * j) * 4;
+          if (m0 < M) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int g = 0; g < kGroups; ++g) {
+              if ((e >> (11 + g)) & 1) {
+                const float *ring = flush + ((g * nepi + ej) * kFlushRing + ((e >> (14 + 2 * g)) & 1)) * gslot_floats;
+#pragma unroll
+                for (int w = 0; w < kWarpsPerGroup; ++w) {
+                  const float4 p = *reinterpret_cast<const float4 *>(ring + (w * kTileRows + row) * mp + m0);
+                  v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+                }
+              }
+            }
+            *reinterpret_cast<float4 *>(vst + row * vp + m0) = v;
+          }
         }
       }
       __syncwarp();
@@ -500,7 +520,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
       bool ok = true;
 #pragma unroll 1
       for (int m = lane >> 4; m < M; m += 2) {
-        float v = vst[row * 16 + m];
+        float v = vst[row * vp + m];
         if (!starts) {
           // continuation of a tile another CTA started: store the partial sums into this
           // CTA's workspace slot (idle words read 0xffffffff); the owner polls them
@@ -572,14 +592,16 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
   if (warp == 0) TTL_MARK(15);
   if (warp == 0 && lane == 0) TST(47, 6);
 
-  // Stage it goes to warp group it % kGroups; the ring depth is a multiple of kGroups, so a
-  // group meets the same slots again and again and follows their barriers phase by phase.
+  // Stage it sits in ring slot it % nst and goes to warp group slot % kGroups: a slot always
+  // belongs to the same group, which therefore follows its barriers phase by phase whatever the
+  // ring depth (a group that tested a barrier it had not followed could see a stale phase
+  // parity, read the slot early and arrive twice on its empty barrier).
   float *fl_base = flush + grp * nepi * kFlushRing * gslot_floats + wq * kTileRows * mp;
   int slot = grp, round = 0;
   int fcnt = 0;  // hand-overs made so far to each epilogue warp: 10 bits each
   int turn = 0;  // stages this group has taken: rotates the pair ranges among its warps
 #pragma unroll 1
-  for (int it = grp; it < nimg; it += kGroups, ++turn) {
+  for (int it = grp; it < nimg; ++turn) {
     const uint32_t e = list[it];
     if (!mbar_wait(smem_u32(&bar_full[slot]), round & 1)) {
       if (lane == 0) atomicExch(status, 4);
@@ -603,8 +625,14 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
     __syncwarp();
     if (lane == 0) mbar_arrive(smem_u32(&bar_empty[slot]));
     if (wq == 0 && lane == 0) TST(it, 2);
-    slot += kGroups;
-    if (slot >= nst) { slot -= nst; ++round; }
+    if (slot + kGroups < nst) {
+      slot += kGroups;
+      it += kGroups;
+    } else {  // on to the group's first slot, one round later
+      it += nst - slot + grp;
+      slot = grp;
+      ++round;
+    }
 
     if (e & kEntFlush) {
       // ---- the group's last stage of this tile: hand the partial sums to the tile's epilogue
@@ -680,19 +708,19 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
   // (M rounded up to 4) partial sums; fewer epilogue warps for large M keep this at 18-24 KB
   const int nepi = h.M <= 4 ? kEpiWarps : (h.M <= 8 ? 2 : 1);
   a.nepi = nepi;
-  const int fl_bytes = kGroups * nepi * kFlushRing * kWarpsPerGroup * kTileRows * ((h.M + 3) & ~3) * 4;
-  const int fixed = fl_bytes + kMetaSegs * kTileRows * 12 + kMaxList * 8 + kEpiWarps * kTileRows * 16 * 4;
-  const int total_budget = 110 * 1024;  // two CTAs (this layer's and the next one's) share an SM
+  const int mp = (h.M <= 3) ? h.M : ((h.M + 3) & ~3);
+  const int fl_bytes = kGroups * nepi * kFlushRing * kWarpsPerGroup * kTileRows * mp * 4;
+  const int fixed = fl_bytes + kMetaSegs * kTileRows * 12 + kMaxList * 8 + kEpiWarps * kTileRows * (h.M <= 4 ? 4 : 16) * 4;
+  const int total_budget = 112 * 1024;  // two CTAs (this layer's and the next one's) share an SM's 228 KB
   int xbytes = h.M * (2 * h.K + 16);
   bool xs = true;
-  // The ring depth must be a multiple of the number of warp groups: then a slot is always
-  // consumed by the same group, whose waits on that slot's barrier follow each other phase
-  // by phase.  (With another depth a group could test a phase parity on a barrier it did not
-  // follow, see a stale "complete", read the slot early and arrive twice on its empty barrier.)
+  // Ring depth: slot s belongs to warp group s % 3, so depths 3k and 3k + 2 split the slots
+  // 1:1:1 and (k+1):(k+1):k; 3k + 1 would leave one group with half as many more slots as the
+  // others and measured slower than 3k.
   auto depth = [&](int xb) {
     int n = (total_budget - fixed - xb) / a.slot_bytes;
     if (n > kMaxStages) n = kMaxStages;
-    return (n / kGroups) * kGroups;
+    return (n % kGroups == 1 && n > kGroups) ? n - 1 : n;
   };
   // activations go to shared memory only while that leaves every warp group two ring slots
   if (xbytes > 44 * 1024 || depth(xbytes) < min(2 * kGroups, depth(0))) {
@@ -765,6 +793,10 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
                                   : reinterpret_cast<const void *>(gemv_tiled_kernel<2, true>);
   if (dev < 64 && smem_set[dev][variant] < smem) {
     RDQ_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    // Always the largest shared-memory carve-out: layers of different footprints follow each
+    // other, and an SM cannot change its carve-out while a CTA of the previous layer is resident
+    // (the next layer's CTA would wait instead of filling its ring alongside).
+    RDQ_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     smem_set[dev][variant] = smem;
   }
 
