@@ -71,10 +71,10 @@ constexpr int kMaxStages = 12;
 constexpr int kChunkMax = RDQ_CHUNK_MAX;  // longest k chunk of an image, in NVFP4 elements
 constexpr int kMaxList = 256;       // images one CTA can stream (stage list entries)
 
-// pitch of a block-scale row inside an NVFP4 image: payload rounded up to 16 B plus a
-// skew that makes the pitch an odd multiple of 16 B (conflict-free 8-row reads)
+// pitch of a block-scale row inside an NVFP4 image: the payload (ck / 16 bytes) rounded up to
+// an odd multiple of 16 B, so that the eight rows a warp reads together fall on distinct banks
 __host__ __device__ inline int scale_pitch(int ck) {
-  int sp = (((ck >> 4) + 15) & ~15) + 16;
+  int sp = ((ck >> 4) + 15) & ~15;
   if (((sp >> 4) & 1) == 0) sp += 16;
   return sp;
 }
