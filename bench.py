@@ -383,7 +383,7 @@ def main() -> None:
     achieved = per_launch_bytes / (ms * 1e-3 / launches) / 1e9
     # dram__bytes_read + dram__bytes_write per launch from the ncu capture summarised in
     # profiles/gemv_tiled_block_m1.md (average over the four fused launches of a step)
-    traffic = 19.85e6 if (m == 1 and not args.no_fuse and args.kernel == "tiled") else None
+    traffic = 19.46e6 if (m == 1 and not args.no_fuse and args.kernel == "tiled") else None
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
