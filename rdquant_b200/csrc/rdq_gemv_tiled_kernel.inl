@@ -78,7 +78,8 @@ struct TiledArgs {
   int status_idx;
   int nstages;
   int slot_bytes;
-  int nepi;  // epilogue warps in use
+  int nepi;    // epilogue warps in use
+  int fdepth;  // slots per hand-over ring
 };
 
 #ifdef RDQ_TIMELINE

@@ -191,9 +191,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
   const int mp = (M <= 3) ? M : ((M + 3) & ~3);  // M > 3: rows of four floats, read 16 B at a time
   const int vp = (M <= 4) ? 4 : 16;               // row pitch of an epilogue warp's staging tile
   const int nepi = a.nepi;      // epilogue warps in use (1..kEpiWarps)
+  const int fdep = a.fdepth;    // slots per hand-over ring (1 or 2)
   const int gslot_floats = kWarpsPerGroup * kTileRows * mp;
   float *flush = reinterpret_cast<float *>(smem + nst * a.slot_bytes);
-  int *meta_col = reinterpret_cast<int *>(flush + kGroups * nepi * kFlushRing * gslot_floats);
+  int *meta_col = reinterpret_cast<int *>(flush + kGroups * nepi * fdep * gslot_floats);
   float *meta_scl = reinterpret_cast<float *>(meta_col + kMetaSegs * kTileRows);
   float *meta_bia = meta_scl + kMetaSegs * kTileRows;
   uint32_t *list = reinterpret_cast<uint32_t *>(meta_bia + kMetaSegs * kTileRows);
@@ -451,8 +452,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
       const bool starts = (e >> 9) & 1, ends = (e >> 10) & 1;
 #pragma unroll
       for (int g = 0; g < kGroups; ++g) {
-        const int code = (e >> (14 + 2 * g)) & 3;
-        if (((e >> (11 + g)) & 1) && !mbar_wait(smem_u32(&fl_full[g][ej][code & 1]), code >> 1)) {
+        const int code = (e >> (14 + 2 * g)) & 3;  // hand-overs before, modulo 4
+        const int fsl = (fdep == 2) ? (code & 1) : 0, fpar = (fdep == 2) ? (code >> 1) : (code & 1);
+        if (((e >> (11 + g)) & 1) && !mbar_wait(smem_u32(&fl_full[g][ej][fsl]), fpar)) {
           if (lane == 0) atomicExch(status, 2);
           return;
         }
@@ -481,7 +483,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
 #pragma unroll
           for (int g = 0; g < kGroups; ++g) {
             if ((e >> (11 + g)) & 1) {
-              const float *ring = flush + ((g * nepi + ej) * kFlushRing + ((e >> (14 + 2 * g)) & 1)) * gslot_floats;
+              const float *ring = flush + ((g * nepi + ej) * fdep + (fdep == 2 ? ((e >> (14 + 2 * g)) & 1) : 0)) * gslot_floats;
 #pragma unroll
               for (int w = 0; w < kWarpsPerGroup; ++w) v += ring[(w * kTileRows + row) * mp + m];
             }
@@ -497,7 +499,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
 #pragma unroll
             for (int g = 0; g < kGroups; ++g) {
               if ((e >> (11 + g)) & 1) {
-                const float *ring = flush + ((g * nepi + ej) * kFlushRing + ((e >> (14 + 2 * g)) & 1)) * gslot_floats;
+                const float *ring = flush + ((g * nepi + ej) * fdep + (fdep == 2 ? ((e >> (14 + 2 * g)) & 1) : 0)) * gslot_floats;
 #pragma unroll
                 for (int w = 0; w < kWarpsPerGroup; ++w) {
                   const float4 p = *reinterpret_cast<const float4 *>(ring + (w * kTileRows + row) * mp + m0);
@@ -513,7 +515,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
       if (lane == 0) {
 #pragma unroll
         for (int g = 0; g < kGroups; ++g)
-          if ((e >> (11 + g)) & 1) mbar_arrive(smem_u32(&fl_empty[g][ej][(e >> (14 + 2 * g)) & 1]));
+          if ((e >> (11 + g)) & 1) mbar_arrive(smem_u32(&fl_empty[g][ej][fdep == 2 ? ((e >> (14 + 2 * g)) & 1) : 0]));
       }
       if (lane == 0) TST(q, 4);
       const int b_hi = (starts && !ends) ? b_last : static_cast<int>(blockIdx.x);
@@ -596,7 +598,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
   // belongs to the same group, which therefore follows its barriers phase by phase whatever the
   // ring depth (a group that tested a barrier it had not followed could see a stale phase
   // parity, read the slot early and arrive twice on its empty barrier).
-  float *fl_base = flush + grp * nepi * kFlushRing * gslot_floats + wq * kTileRows * mp;
+  float *fl_base = flush + grp * nepi * fdep * gslot_floats + wq * kTileRows * mp;
   int slot = grp, round = 0;
   int fcnt = 0;  // hand-overs made so far to each epilogue warp: 10 bits each
   int turn = 0;  // stages this group has taken: rotates the pair ranges among its warps
@@ -640,12 +642,12 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
       const int ej = (e >> 11) & 3;
       const int cnt = (fcnt >> (10 * ej)) & 1023;
       fcnt += 1 << (10 * ej);
-      const int fslot = cnt & 1, fround = cnt >> 1;
+      const int fslot = (fdep == 2) ? (cnt & 1) : 0, fround = (fdep == 2) ? (cnt >> 1) : cnt;
       if (fround > 0 && !mbar_wait(smem_u32(&fl_empty[grp][ej][fslot]), (fround - 1) & 1)) {
         if (lane == 0) atomicExch(status, 5);
         return;
       }
-      float *buf = fl_base + (ej * kFlushRing + fslot) * gslot_floats;
+      float *buf = fl_base + (ej * fdep + fslot) * gslot_floats;
 #pragma unroll
       for (int n = 0; n < NT; ++n) {
 #pragma unroll
@@ -706,10 +708,14 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
   // shared memory: weight ring | flush ring | output metadata | activations (if they fit)
   // hand-over rings: (3 groups x nepi epilogue warps) x kFlushRing slots of 4 warps x 16 rows x
   // (M rounded up to 4) partial sums; fewer epilogue warps for large M keep this at 18-24 KB
-  const int nepi = h.M <= 4 ? kEpiWarps : (h.M <= 8 ? 2 : 1);
+  // up to four activation rows: 3 epilogue warps, 2-slot rings (18 KB at most); up to eight:
+  // 3 warps, 1-slot rings (18 KB); beyond: 2 warps, 1-slot rings (24 KB)
+  const int nepi = h.M <= 8 ? kEpiWarps : 2;
+  const int fdep = h.M <= 4 ? kFlushRing : 1;
   a.nepi = nepi;
+  a.fdepth = fdep;
   const int mp = (h.M <= 3) ? h.M : ((h.M + 3) & ~3);
-  const int fl_bytes = kGroups * nepi * kFlushRing * kWarpsPerGroup * kTileRows * mp * 4;
+  const int fl_bytes = kGroups * nepi * fdep * kWarpsPerGroup * kTileRows * mp * 4;
   const int fixed = fl_bytes + kMetaSegs * kTileRows * 12 + kMaxList * 8 + kEpiWarps * kTileRows * (h.M <= 4 ? 4 : 16) * 4;
   const int total_budget = 112 * 1024;  // two CTAs (this layer's and the next one's) share an SM's 228 KB
   int xbytes = h.M * (2 * h.K + 16);
