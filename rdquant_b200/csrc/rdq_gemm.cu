@@ -2,8 +2,8 @@
 // sm_100a: dequantise-to-shared-memory producers feeding tcgen05 kind::f16 MMAs with the
 // FP32 accumulator in tensor memory.
 //
-// Tile: 128 or 256 tokens x 128 or 256 output channels per CTA (the largest that still gives
-// every SM a CTA), k blocks of 64.  The output tile is taken in ORIGINAL channel order:
+// Tile: 128 or 256 tokens x 128 or 256 output channels per CTA (chosen per launch by a time
+// estimate, see gemm_plan), k blocks of 64.  The output tile is taken in ORIGINAL channel order:
 // channel n0 + j reads permuted row inv_perm[n0 + j], so the permutation costs nothing on the
 // store side (rows of all three formats meet in one tile).
 //
