@@ -291,6 +291,7 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
     if (warp - 2 < kEpiWarps) {
       const bool ok = gemm_wait(&S.accum, 0, &S.abort_flag);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (threadIdx.x == 64) GTL(126, 0);
       const int q = warp & 3;  // tensor-memory lane quarter this warp may read
       const int sub = (warp - 2) >> 2;
       if (ok) {
@@ -341,6 +342,7 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
     }
   }
 
+  if (threadIdx.x == 64) GTL(127, 0);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
