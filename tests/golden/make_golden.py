@@ -1,9 +1,9 @@
 """Generate the golden fixtures of tests/golden/ by RUNNING THE REFERENCE PACKAGE.
 
-Needs the reference checkout (default /root/reference, override with RDQUANT_REFERENCE);
-it is not needed to run the tests, only to regenerate the fixtures:
+Needs a checkout of the reference package, named by the environment variable
+RDQUANT_REFERENCE; it is not needed to run the tests, only to regenerate the fixtures:
 
-    python tests/golden/make_golden.py
+    RDQUANT_REFERENCE=<path to the RDQuant checkout> python tests/golden/make_golden.py
 
 Writes
   tables.npz        E4M3 decode table from torch.float8_e4m3fn, the reference's NVFP4 LUT,
@@ -23,7 +23,9 @@ import tempfile
 import numpy as np
 import torch
 
-REF = os.environ.get("RDQUANT_REFERENCE", "/root/reference")
+REF = os.environ.get("RDQUANT_REFERENCE")
+if not REF:
+    raise SystemExit("set RDQUANT_REFERENCE to the RDQuant checkout the fixtures are generated from")
 sys.path.insert(0, REF)
 
 from rdquant.core import formats as rf  # noqa: E402
