@@ -25,8 +25,9 @@
 //                       and read 32 / 64 / 128 contiguous bytes.
 //   epilogue            twelve of those warps: tcgen05.ld of the accumulators (a warp reads
 //                       the 32 tensor-memory lanes of its quarter, the warps of a quarter
-//                       take the 32-column chunks in turn), channel scale and bias, f16
-//                       conversion, 64-byte vector stores.
+//                       take pairs of 32-column chunks in turn), channel scale and bias, f16
+//                       conversion, transposition through the free stage buffers, stores of
+//                       4 rows x 128 contiguous bytes per instruction.
 //
 // Shared memory: 4 stages x (16 or 32 KB A + 16 KB B), or 3 x (32 KB A + 32 KB B) for the
 // 256 x 256 tile.  All mbarrier waits are bounded; a wait that runs out raises an abort flag

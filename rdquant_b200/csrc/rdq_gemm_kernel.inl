@@ -288,6 +288,7 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
     // A warp may read the tensor-memory lanes 32 (warp % 4) ...; the producer warps that share a
     // lane quarter take the 32-column chunks of the accumulators in turn.
     constexpr int kEpiWarps = (Cfg::kProducerWarps / 4) * 4;  // whole sets of four warps
+    constexpr int kEpiPitch = 144;  // staging row pitch in bytes: 128 B payload, odd multiple of 16 B
     if (warp - 2 < kEpiWarps) {
       const bool ok = gemm_wait(&S.accum, 0, &S.abort_flag);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -296,9 +297,15 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
       const int sub = (warp - 2) >> 2;
       if (ok) {
 #pragma unroll 1
-        for (int ci = sub; ci < MT * (BN / 32); ci += kEpiWarps / 4) {
-          const int mt = ci / (BN / 32), cc = ci % (BN / 32);
+        // a warp takes pairs of adjacent 32-channel chunks: 64 channels = 128 B of an output row
+        for (int cp = sub; cp < MT * (BN / 64); cp += kEpiWarps / 4) {
+          const int mt = cp / (BN / 64);
           const int m = m0 + mt * BM + q * 32 + lane;
+          const bool wide = a.ksplit == 1 && n0 + (cp % (BN / 64)) * 64 + 64 <= N && (N & 7) == 0;
+          const uint32_t stg = a_base + static_cast<uint32_t>(warp - 2) * (32 * kEpiPitch);
+#pragma unroll 1
+          for (int hh = 0; hh < 2; ++hh) {
+          const int cc = (cp % (BN / 64)) * 2 + hh;
           uint32_t r[32];
           tmem_ld32(tmem + (static_cast<uint32_t>(q * 32) << 16) + mt * BN + cc * 32, r);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -314,28 +321,49 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
               for (int e = 0; e < 32; ++e)
                 if (n0 + cc * 32 + e < N) dst[e] = __uint_as_float(r[e]);
             }
+          } else if (wide) {
+            // Whole 64-channel pair: the warp turns its 32 rows x 128 B around in shared memory
+            // (the stage buffers are free once the accumulators are complete) so that a store
+            // instruction writes four rows x 128 contiguous bytes instead of 32 rows x 16 B:
+            // the stores of a tile otherwise take three times as long as the rest of its epilogue.
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint32_t o[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int c = cc * 32 + v * 8 + e * 2;
+                const float f0 = fmaf(__uint_as_float(r[v * 8 + e * 2]), S.colscale[c], S.colbias[c]);
+                const float f1 = fmaf(__uint_as_float(r[v * 8 + e * 2 + 1]), S.colscale[c + 1], S.colbias[c + 1]);
+                const __half2 h = __floats2half2_rn(f0, f1);
+                o[e] = *reinterpret_cast<const uint32_t *>(&h);
+              }
+              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(stg + lane * kEpiPitch + hh * 64 + v * 16), "r"(o[0]),
+                           "r"(o[1]), "r"(o[2]), "r"(o[3])
+                           : "memory");
+            }
           } else if (m < a.M) {
             __half *dst = a.y + 1ll * m * N + n0 + cc * 32;
-            if (n0 + cc * 32 + 32 <= N && (N & 7) == 0) {
-#pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                uint32_t o[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const int c = cc * 32 + v * 8 + e * 2;
-                  const float f0 = fmaf(__uint_as_float(r[v * 8 + e * 2]), S.colscale[c], S.colbias[c]);
-                  const float f1 = fmaf(__uint_as_float(r[v * 8 + e * 2 + 1]), S.colscale[c + 1], S.colbias[c + 1]);
-                  const __half2 h = __floats2half2_rn(f0, f1);
-                  o[e] = *reinterpret_cast<const uint32_t *>(&h);
-                }
-                *reinterpret_cast<uint4 *>(dst + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
-              }
-            } else {
-              for (int e = 0; e < 32; ++e) {
-                const int c = cc * 32 + e;
-                if (n0 + c < N) dst[e] = __float2half_rn(fmaf(__uint_as_float(r[e]), S.colscale[c], S.colbias[c]));
-              }
+            for (int e = 0; e < 32; ++e) {
+              const int c = cc * 32 + e;
+              if (n0 + c < N) dst[e] = __float2half_rn(fmaf(__uint_as_float(r[e]), S.colscale[c], S.colbias[c]));
             }
+          }
+          }  // hh
+          if (wide) {
+            __syncwarp();
+            const int m_base = m0 + mt * BM + q * 32;
+            const int c0 = (cp % (BN / 64)) * 64;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int row = i * 4 + (lane >> 3), piece = lane & 7;
+              uint4 val;
+              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                           : "r"(stg + row * kEpiPitch + piece * 16)
+                           : "memory");
+              if (m_base + row < a.M) *reinterpret_cast<uint4 *>(a.y + 1ll * (m_base + row) * N + n0 + c0 + piece * 8) = val;
+            }
+            __syncwarp();
           }
         }
       }
