@@ -180,6 +180,10 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
   const int kb0 = static_cast<int>(1ll * blockIdx.z * nkb_all / a.ksplit);
   const int nkb = static_cast<int>(1ll * (blockIdx.z + 1) * nkb_all / a.ksplit);
 
+  if (tid == 32) {
+    // the TMA unit reads the tensor map from memory: start that fetch now
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&xmap)) : "memory");
+  }
   if (tid == 0) {
     for (int i = 0; i < NS; ++i) {
       mbar_init(smem_u32(&S.full[i]), Cfg::kProducers + 1);
