@@ -13,7 +13,7 @@
 //                       128-token accumulator, commits the stage back to the producers,
 //                       finally commits the accumulators.  The warp also owns the
 //                       tensor-memory allocation (up to all 512 columns).
-//   warps 2..           12 or 14 dequantisation warps.  The rows of the tile are sorted by
+//   warps 2..           12 or 22 dequantisation warps.  The rows of the tile are sorted by
 //                       format and padded to groups of four; a warp takes every W-th group,
 //                       a quarter warp one row, a lane one 16-byte chunk (8 k) of it: it
 //                       loads the next k block's 4 / 8 / 16 packed bytes into registers,
@@ -58,10 +58,13 @@ constexpr int kMaxBN = 256;
 // accumulators per CTA.  Producer warps convert groups of four weight rows (a quarter warp per
 // row); kTasks = groups a warp handles per k block.
 //   <1,128> <2,128>: 12 producer warps, 4 stages         (small problems)
-//   <2,256>        : 14 producer warps, 3 x 64 KB stages, all 512 tensor-memory columns
+//   <2,256>        : 22 producer warps (768 threads), 3 x 64 KB stages, all 512 tensor-memory columns
+#ifndef RDQ_GEMM_PW
+#define RDQ_GEMM_PW 22
+#endif
 template <int MT, int BN>
 struct GemmCfg {
-  static constexpr int kProducerWarps = (BN == 128) ? 12 : 14;
+  static constexpr int kProducerWarps = (BN == 128) ? 12 : RDQ_GEMM_PW;
   static constexpr int kProducers = kProducerWarps * 32;
   static constexpr int kThreads = (2 + kProducerWarps) * 32;
   static constexpr int kStageB = BN * BK * 2;

@@ -30,9 +30,12 @@ struct StageCursor {
   __device__ __forceinline__ void begin(GemmSmem &S) {
     if (ph > 0 && alive) alive = gemm_wait(&S.empty[s], (ph - 1) & 1, &S.abort_flag);
   }
+  // every lane fences its own writes; one arrival per warp (hundreds of arrivals per stage on
+  // one barrier were the slowest part of a k block)
   __device__ __forceinline__ void end(GemmSmem &S) {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    mbar_arrive(smem_u32(&S.full[s]));
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&S.full[s]));
     if (++s == NS) { s = 0; ++ph; }
   }
 };
@@ -186,7 +189,7 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
   }
   if (tid == 0) {
     for (int i = 0; i < NS; ++i) {
-      mbar_init(smem_u32(&S.full[i]), Cfg::kProducers + 1);
+      mbar_init(smem_u32(&S.full[i]), Cfg::kProducerWarps + 1);  // producer warps + the TMA thread
       mbar_init(smem_u32(&S.empty[i]), 1);
     }
     mbar_init(smem_u32(&S.accum), 1);
