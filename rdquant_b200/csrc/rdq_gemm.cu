@@ -34,8 +34,9 @@
 // that every role checks, and the kernel drains and frees its tensor memory.
 //
 // Measured on B200 (in-kernel clocks, 256 x 256 tile): with the weight conversion switched
-// off the pipeline runs at the MMA rate (1024 cycles per k block); with it, 1450 cycles --
-// the conversion warps' instruction issue is the bound, not L2 or shared-memory bandwidth.
+// off the pipeline runs at the MMA rate (1024 cycles per k block); with it, about 1450 cycles.
+// Shared-memory bandwidth is the bound: per k block the MMAs read 96 KB (A and B once per
+// M128 instruction), TMA writes 32 KB and the producers 32 KB = 160 KB at 128 B/clk.
 //
 // FLOPs per launch: 2*M*N*K.  Bound: dense f16 tensor throughput.
 //

@@ -122,36 +122,32 @@ __device__ __forceinline__ void produce_rows(GemmSmem &S, const GemmArgs &a, uin
     for (int p = 0; p < PF; ++p) {
       const int kb = kbase + p;
       if (kb >= nkb) break;
-      uint4 c[TMAX];
-#pragma unroll
-      for (int t = 0; t < TMAX; ++t) c[t] = q[p][t];
-      if (kb + PF < nkb) {
-#pragma unroll
-        for (int t = 0; t < TMAX; ++t) q[p][t] = load(t, kb + PF);
-      }
       if (threadIdx.x == 64) GTL(kb, 3);
       cur.begin(S);
       if (threadIdx.x == 64) GTL(kb, 4);
       const uint32_t sbase = b_base + cur.s * SB;
+      // convert straight out of the prefetch registers, then refill them for k block kb + PF
 #pragma unroll
       for (int t = 0; t < TMAX; ++t) {
+        const uint4 c = q[p][t];
         uint32_t o0 = 0u, o1 = 0u, o2 = 0u, o3 = 0u;
         if (fmt[t] == 0) {
-          const uint32_t scl = __byte_perm(cvt_e4m3x2(c[t].y), 0u, 0x1010u);
-          cvt_e2m1x8(c[t].x, o0, o1, o2, o3);
+          const uint32_t scl = __byte_perm(cvt_e4m3x2(c.y), 0u, 0x1010u);
+          cvt_e2m1x8(c.x, o0, o1, o2, o3);
           o0 = hmul2_u32(o0, scl);
           o1 = hmul2_u32(o1, scl);
           o2 = hmul2_u32(o2, scl);
           o3 = hmul2_u32(o3, scl);
         } else if (fmt[t] == 1) {
-          cvt_e4m3x4(c[t].x, o0, o1);
-          cvt_e4m3x4(c[t].y, o2, o3);
+          cvt_e4m3x4(c.x, o0, o1);
+          cvt_e4m3x4(c.y, o2, o3);
         } else if (fmt[t] == 2) {
-          o0 = c[t].x; o1 = c[t].y; o2 = c[t].z; o3 = c[t].w;
+          o0 = c.x; o1 = c.y; o2 = c.z; o3 = c.w;
         }
         if (fmt[t] != 4)
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sbase + roff[t]), "r"(o0), "r"(o1), "r"(o2), "r"(o3)
                        : "memory");
+        if (kb + PF < nkb) q[p][t] = load(t, kb + PF);
       }
       cur.end(S);
       if (threadIdx.x == 64) GTL(kb, 5);
