@@ -13,6 +13,7 @@ namespace {
 __global__ void __launch_bounds__(256) stage_copy_kernel(uint8_t *__restrict__ dst, const uint8_t *__restrict__ src,
                                                          size_t bytes) {
   pdl_launch_dependents();  // a dependent launch may start its own prologue now
+  pdl_wait();               // launched early itself: the producer of src must be complete
   const size_t n16 = bytes >> 4;
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += stride)
@@ -26,8 +27,21 @@ int launch_stage_copy(void *dst, const void *src, size_t bytes, cudaStream_t str
   if (bytes == 0) return RDQ_OK;
   size_t blocks = (bytes + 256 * 16 - 1) / (256 * 16);
   if (blocks > 64) blocks = 64;
-  stage_copy_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<uint8_t *>(dst), static_cast<const uint8_t *>(src),
-                                                                       bytes);
+  // launched with programmatic stream serialization: the kernel may become resident while its
+  // predecessor drains and waits for it inside (griddepcontrol.wait)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+  cfg.blockDim = dim3(256);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  uint8_t *d = static_cast<uint8_t *>(dst);
+  const uint8_t *sp = static_cast<const uint8_t *>(src);
+  void *params[3] = {&d, &sp, &bytes};
+  RDQ_CUDA(cudaLaunchKernelExC(&cfg, reinterpret_cast<const void *>(stage_copy_kernel), params));
   RDQ_CUDA(cudaGetLastError());
   return RDQ_OK;
 }
