@@ -728,8 +728,9 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
     if (n > kMaxStages) n = kMaxStages;
     return (n % kGroups == 1 && n > kGroups) ? n - 1 : n;
   };
-  // activations go to shared memory only while that leaves every warp group two ring slots
-  if (xbytes > 44 * 1024 || depth(xbytes) < min(2 * kGroups, depth(0))) {
+  // activations go to shared memory while that leaves every warp group a ring slot: reading
+  // them through L1 costs more than a shallower ring (measured for M = 3 .. 8)
+  if (xbytes > 44 * 1024 || depth(xbytes) < min(kGroups, depth(0))) {
     xs = false;
     xbytes = 0;
   }
