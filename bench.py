@@ -250,8 +250,7 @@ def main() -> None:
     ap.add_argument("--copies", type=int, default=6, help="rotating weight copies (L2 defeat)")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--kernel", default="tiled", choices=["tiled", "stream", "generic"])
-    ap.add_argument("--no-l2-prefetch", action="store_true")
+    ap.add_argument("--kernel", default="tiled", choices=["tiled", "generic"])
     ap.add_argument("--no-fuse", action="store_true", help="seven launches per step instead of four")
     ap.add_argument("--prefill", type=int, default=0, metavar="TOKENS",
                     help="measure the tcgen05 prefill GEMM at this many tokens instead of the decode GEMV")
@@ -285,11 +284,9 @@ def main() -> None:
     copies = max(args.copies, 2)
     layers = build_block(device, seed=rank, copies=copies, fuse=not args.no_fuse)
     step_bytes = sum(l["bytes"] for l in layers)
-    flags = {"tiled": _lib.RDQ_GEMV_AUTO, "stream": _lib.RDQ_GEMV_STREAM, "generic": _lib.RDQ_GEMV_GENERIC}[args.kernel]
+    flags = {"tiled": _lib.RDQ_GEMV_AUTO, "generic": _lib.RDQ_GEMV_GENERIC}[args.kernel]
     if not args.no_pdl:
         flags |= _lib.RDQ_GEMV_PDL
-    if args.no_l2_prefetch:
-        flags |= _lib.RDQ_GEMV_NO_L2_PREFETCH
 
     gen = torch.Generator().manual_seed(1234 + rank)
     xs = [torch.randn(m, l["k"], generator=gen).half().to(device) for l in layers]

@@ -8,9 +8,13 @@
  *     NULL = legacy default stream) of the CURRENT device,
  *   - return 0 on success and a negative RDQ_E_* code on failure, with a
  *     human readable message available from rdq_last_error() (thread local),
- *   - keep no global state; the only cross-launch state is the caller-owned
- *     `counters` array of the stream GEMV, which must be zero on first use and
- *     is returned to zero by every launch that completes.
+ *   - may be called from several host threads; state that outlives a launch is
+ *     limited to: the caller-owned scratch of the GEMVs (`workspace` idle
+ *     pattern, `counters` zero between launches), per-device caches of device
+ *     attributes inside the library, the device array of
+ *     rdq_gemv_tiled_noalloc, and one status word per device for the GEMM.
+ *     A kernel whose bounded device-side wait runs out leaves a non-zero status
+ *     word behind; the rdq_*_status calls below turn that into RDQ_E_DEVICE.
  *
  * Tensor layouts are the packed-checkpoint layouts of the reference
  * (rdquant/integrations/hf_export.py:58-125), rows in permuted
@@ -73,9 +77,12 @@ int rdq_dequant_packed(const void *w_fp4, const void *w_fp4_scales,
                        void *stream);
 
 /*
- * Scratch the stream GEMV needs for a layer of N output channels on the
- * current device: `*workspace_bytes` of float scratch (contents irrelevant)
- * and `*counter_bytes` of int32 counters (must start zeroed).
+ * Scratch rdq_gemv_tiled needs on the current device (the same for every
+ * layer; N is accepted for symmetry with the reference's per-layer workspace,
+ * rdquant/fused_gemv_pack.py:343-349): `*workspace_bytes` of float scratch,
+ * one 16 x 16 slot per CTA of the grid (148 KB on a 148-SM GPU; every 32-bit
+ * word must read 0xffffffff on first use), and
+ * `*counter_bytes` of int32 counters (must start zeroed).
  */
 int rdq_gemv_scratch_size(int N, size_t *workspace_bytes, size_t *counter_bytes);
 
@@ -89,20 +96,23 @@ int rdq_gemv_scratch_size(int N, size_t *workspace_bytes, size_t *counter_bytes)
  *   x     f16 [M, K] row-major (ldx = K)
  *   y     f16 [M, N] row-major, every element written
  *   bias  f16 [N] in original channel order, or NULL
- *   workspace / counters: from rdq_gemv_scratch_size; may both be NULL, in
- *     which case only the self-contained kernel (no K split) is used.
+ *   workspace / counters: unused by this entry point (it runs the any-shape
+ *     kernel, one warp per output channel, on the row-major tensors); they
+ *     are the scratch of rdq_gemv_tiled.  May be NULL.
  *   flags: RDQ_GEMV_* below.
  * FP32 accumulation; NVFP4 weights enter the product as f16(LUT*scale)
  * (exact), FP8 weights as f16(e4m3) with the channel scale applied to the
  * FP32 sum.  Deterministic: repeated calls give identical bits.
  */
-#define RDQ_GEMV_AUTO        0   /* pick stream kernel when the shape allows */
+#define RDQ_GEMV_AUTO        0   /* default kernel choice                    */
 #define RDQ_GEMV_GENERIC     1   /* force the any-shape kernel               */
-#define RDQ_GEMV_STREAM      2   /* force the TMA-staged stream kernel       */
 #define RDQ_GEMV_PDL         16  /* launch with programmatic dependent launch:
                                     weights are prefetched before the wait on
                                     the preceding kernel, x is read after it */
-#define RDQ_GEMV_NO_L2_PREFETCH 32 /* stream kernel: skip the bulk L2 prefetch */
+#define RDQ_GEMV_TEST_TIMEOUT 64 /* tiled kernels, self-test: after its work one
+                                    warp of CTA 0 waits, for a fraction of a
+                                    millisecond, on a barrier nothing completes
+                                    and reports the expired wait (status 9) */
 int rdq_gemv_mixed(const void *x, int M,
                    const void *w_fp4, const void *w_fp4_scales,
                    float w_fp4_global_scale,
@@ -118,10 +128,13 @@ int rdq_gemv_mixed(const void *x, int M,
  * Tiled weight layout of the fast decode GEMV.  rdq_gemv_repack re-tiles the
  * row-major checkpoint tensors once per layer into `w_tiled`
  * (rdq_gemv_tiled_bytes bytes; 0 = shape has no tiled layout: groups must be
- * multiples of 16 rows and K must split into equal chunks that are multiples
- * of 64).  16 rows x one k chunk are stored as one contiguous block that is
- * copied to shared memory by a single bulk-async (TMA) copy.  Plays the role
- * of the reference's load-time Marlin repack
+ * multiples of 16 rows, K must split into equal chunks of at most 2048
+ * elements that are multiples of 64, and a tile may have at most 256 chunks).
+ * 16 rows x one k chunk are stored as one contiguous block (rows skewed by 16
+ * bytes against shared-memory bank conflicts) that is copied to shared memory
+ * by a single bulk-async (TMA) copy.  Plays the role of the reference's
+ * load-time
+ * Marlin repack
  * (rdquant/fused_gemv_pack.py:151-172, :310-354).
  */
 size_t rdq_gemv_tiled_bytes(int n_fp4, int n_fp8, int n_fp16, int K);
@@ -141,7 +154,7 @@ int rdq_gemv_repack(const void *w_fp4, const void *w_fp4_scales,
  * use; counters[SM count] is a status word that stays 0 unless a bounded
  * device-side wait ran out.  Launches sharing one workspace / counters pair
  * must be ordered on one stream.
- * flags: RDQ_GEMV_PDL.
+ * flags: RDQ_GEMV_PDL, RDQ_GEMV_TEST_TIMEOUT.
  */
 int rdq_gemv_tiled(const void *x, int M,
                    const void *w_tiled, const float *w_fp8_scales,
@@ -167,7 +180,9 @@ int rdq_gemv_tiled(const void *x, int M,
  * it on `stream`; make that first call before any stream capture begins.  All
  * calls on a device share the one array: calls that may overlap on the GPU
  * (different streams, no ordering) race on it and must be serialised by the
- * caller.  Results are identical to rdq_gemv_tiled.
+ * caller.  Results are identical to rdq_gemv_tiled as long as no launch gave
+ * up a wait; rdq_gemv_tiled_noalloc_status reports that and restores the array.
+ * Set-up is guarded by a mutex: concurrent first calls are safe.
  */
 int rdq_gemv_tiled_noalloc(const void *x, int M,
                            const void *w_tiled, const float *w_fp8_scales,
@@ -176,6 +191,28 @@ int rdq_gemv_tiled_noalloc(const void *x, int M,
                            void *y,
                            int n_fp4, int n_fp8, int n_fp16, int K,
                            int flags, void *stream);
+
+/*
+ * Device-side error reporting.  Every wait inside the kernels is bounded; a
+ * kernel that gives one up records a code in a status word and drains instead
+ * of hanging, and its results are invalid.  These calls synchronise `stream`,
+ * read the status word and return RDQ_OK or RDQ_E_DEVICE (rdq_last_error()
+ * names the wait).  With reset != 0 they also put the scratch back to its idle
+ * state (status and flags zero, every partial-sum slot 0xffffffff), so that the
+ * next launch starts clean.  None of them allocates.  The reference has no
+ * counterpart: its launchers return void and check nothing
+ * (rdquant/csrc/fused_gemv.cu:2049-2078).
+ *   rdq_gemv_tiled_status          caller scratch of rdq_gemv_tiled
+ *   rdq_gemv_tiled_noalloc_status  the library array of rdq_gemv_tiled_noalloc
+ *   rdq_gemm_status                rdq_gemm_mixed / rdq_gemm_mixed_ws (one word
+ *                                  per device)
+ * rdq_gemm_test_timeout(1) makes later GEMM launches end with a wait that runs
+ * out (self-test of this path, like RDQ_GEMV_TEST_TIMEOUT); 0 switches it off.
+ */
+int  rdq_gemv_tiled_status(void *workspace, int32_t *counters, int reset, void *stream);
+int  rdq_gemv_tiled_noalloc_status(int reset, void *stream);
+int  rdq_gemm_status(int reset, void *stream);
+void rdq_gemm_test_timeout(int enable);
 
 /*
  * Prefill GEMM, any M >= 1 (meant for M >= 16):

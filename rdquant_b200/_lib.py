@@ -18,13 +18,12 @@ SOURCES = [
     "rdq_api.cu",
     "rdq_dequant.cu",
     "rdq_gemv_generic.cu",
-    "rdq_gemv_stream.cu",
     "rdq_gemv_tiled.cu",
     "rdq_gemm.cu",
     "rdq_quantize.cu",
     "rdq_stage.cu",
 ]
-HEADERS = ["rdq_common.cuh", "rdq_kernels.cuh", "rdq_gemv_tiled_kernel.inl", "rdq_gemv_tiled_kernel2.inl", "rdq_gemm_kernel.inl",
+HEADERS = ["rdq_common.cuh", "rdq_kernels.cuh", "rdq_gemv_tiled_kernel.inl", "rdq_gemm_kernel.inl",
            os.path.join("..", "..", "include", "rdq_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -34,9 +33,9 @@ NVCC_FLAGS = [
 
 RDQ_GEMV_AUTO = 0
 RDQ_GEMV_GENERIC = 1
-RDQ_GEMV_STREAM = 2
 RDQ_GEMV_PDL = 16
-RDQ_GEMV_NO_L2_PREFETCH = 32
+RDQ_GEMV_TEST_TIMEOUT = 64
+RDQ_E_DEVICE = -4
 
 _lock = threading.Lock()
 _lib = None
@@ -90,6 +89,14 @@ def _bind(lib: ctypes.CDLL) -> None:
     lib.rdq_gemv_tiled.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp]
     lib.rdq_gemv_tiled_noalloc.restype = i32
     lib.rdq_gemv_tiled_noalloc.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+    lib.rdq_gemv_tiled_status.restype = i32
+    lib.rdq_gemv_tiled_status.argtypes = [vp, vp, i32, vp]
+    lib.rdq_gemv_tiled_noalloc_status.restype = i32
+    lib.rdq_gemv_tiled_noalloc_status.argtypes = [i32, vp]
+    lib.rdq_gemm_status.restype = i32
+    lib.rdq_gemm_status.argtypes = [i32, vp]
+    lib.rdq_gemm_test_timeout.restype = None
+    lib.rdq_gemm_test_timeout.argtypes = [i32]
     lib.rdq_gemm_mixed.restype = i32
     lib.rdq_gemm_mixed.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
     lib.rdq_gemm_mixed_ws.restype = i32
@@ -114,6 +121,10 @@ EXPORTS = [
     "rdq_gemv_repack",
     "rdq_gemv_tiled",
     "rdq_gemv_tiled_noalloc",
+    "rdq_gemv_tiled_status",
+    "rdq_gemv_tiled_noalloc_status",
+    "rdq_gemm_status",
+    "rdq_gemm_test_timeout",
     "rdq_gemm_mixed",
     "rdq_gemm_mixed_ws",
     "rdq_gemm_workspace_size",

@@ -17,13 +17,13 @@ void set_error(const char *fmt, ...) {
 }
 
 int sm_count() {
-  static int cached[64] = {};
+  static std::atomic<int> cached[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 1;
-  if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+  if (dev >= 0 && dev < 64 && cached[dev].load() > 0) return cached[dev].load();
   int n = 0;
   if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
-  if (dev >= 0 && dev < 64) cached[dev] = n;
+  if (dev >= 0 && dev < 64) cached[dev].store(n);
   return n;
 }
 
@@ -79,7 +79,8 @@ int rdq_dequant_packed(const void *w_fp4, const void *w_fp4_scales, float w_fp4_
 
 int rdq_gemv_scratch_size(int N, size_t *workspace_bytes, size_t *counter_bytes) {
   RDQ_REQUIRE(N >= 0 && workspace_bytes && counter_bytes, RDQ_E_INVALID, "bad arguments to rdq_gemv_scratch_size");
-  gemv_stream_scratch(N, workspace_bytes, counter_bytes);
+  (void)N;
+  gemv_tiled_scratch(workspace_bytes, counter_bytes);
   return RDQ_OK;
 }
 
@@ -113,16 +114,7 @@ int rdq_gemv_mixed(const void *x, int M, const void *w_fp4, const void *w_fp4_sc
   a.K = K;
   a.workspace = static_cast<float *>(workspace);
   a.counters = counters;
-  const int mode = flags & 15;
-  const bool pdl = (flags & RDQ_GEMV_PDL) != 0;
-  const bool can_stream = gemv_stream_supported(a);
-  if (mode == RDQ_GEMV_STREAM) {
-    RDQ_REQUIRE(can_stream, RDQ_E_UNSUPPORTED,
-                "stream GEMV needs K %% 256 == 0, groups in multiples of 16 rows and scratch buffers "
-                "(K=%d, n=%d/%d/%d)", K, n_fp4, n_fp8, n_fp16);
-  }
-  if (mode != RDQ_GEMV_GENERIC && can_stream)
-    return launch_gemv_stream(a, pdl, (flags & RDQ_GEMV_NO_L2_PREFETCH) == 0, static_cast<cudaStream_t>(stream));
+  (void)flags;
   return launch_gemv_generic(a, static_cast<cudaStream_t>(stream));
 }
 
@@ -172,6 +164,7 @@ int rdq_gemv_tiled(const void *x, int M, const void *w_tiled, const float *w_fp8
   a.K = K;
   a.workspace = static_cast<float *>(workspace);
   a.flags = counters;
+  a.test_timeout = (flags & RDQ_GEMV_TEST_TIMEOUT) ? 1 : 0;
   return launch_gemv_tiled(a, (flags & RDQ_GEMV_PDL) != 0, static_cast<cudaStream_t>(stream));
 }
 
@@ -202,8 +195,22 @@ int rdq_gemv_tiled_noalloc(const void *x, int M, const void *w_tiled, const floa
   a.K = K;
   a.workspace = nullptr;
   a.flags = nullptr;
+  a.test_timeout = (flags & RDQ_GEMV_TEST_TIMEOUT) ? 1 : 0;
   return gemv_tiled_noalloc(a, (flags & RDQ_GEMV_PDL) != 0, static_cast<cudaStream_t>(stream));
 }
+
+int rdq_gemv_tiled_status(void *workspace, int32_t *counters, int reset, void *stream) {
+  RDQ_REQUIRE(workspace != nullptr && counters != nullptr, RDQ_E_INVALID, "workspace and counters must not be null");
+  return gemv_tiled_status(static_cast<float *>(workspace), counters, reset != 0, static_cast<cudaStream_t>(stream));
+}
+
+int rdq_gemv_tiled_noalloc_status(int reset, void *stream) {
+  return gemv_tiled_status(nullptr, nullptr, reset != 0, static_cast<cudaStream_t>(stream));
+}
+
+int rdq_gemm_status(int reset, void *stream) { return gemm_status(reset != 0, static_cast<cudaStream_t>(stream)); }
+
+void rdq_gemm_test_timeout(int enable) { gemm_set_test_timeout(enable != 0); }
 
 int rdq_gemm_mixed_ws(const void *x, int M, const void *w_fp4, const void *w_fp4_scales,
                       float w_fp4_global_scale, const void *w_fp8, const float *w_fp8_scales,

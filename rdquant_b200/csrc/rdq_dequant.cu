@@ -29,8 +29,10 @@ struct DequantArgs {
   int n4, n8, n16, K;
 };
 
-__device__ __forceinline__ void store16(__half *dst, const float (&v)[16], int valid) {
-  if (valid == 16) {
+// `vec` says the row pitch keeps every 16-element run 32 / 64-byte aligned (K % 16 == 0);
+// otherwise the run is stored element by element, full runs included.
+__device__ __forceinline__ void store16(__half *dst, const float (&v)[16], int valid, bool vec) {
+  if (vec) {
     __half2 o[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) o[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
@@ -41,8 +43,8 @@ __device__ __forceinline__ void store16(__half *dst, const float (&v)[16], int v
     for (int i = 0; i < valid; ++i) dst[i] = __float2half_rn(v[i]);
   }
 }
-__device__ __forceinline__ void store16(float *dst, const float (&v)[16], int valid) {
-  if (valid == 16) {
+__device__ __forceinline__ void store16(float *dst, const float (&v)[16], int valid, bool vec) {
+  if (vec) {
     float4 *d4 = reinterpret_cast<float4 *>(dst);
 #pragma unroll
     for (int i = 0; i < 4; ++i) d4[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -114,7 +116,7 @@ __global__ void __launch_bounds__(256) dequant_kernel(DequantArgs a) {
         for (int i = 0; i < valid; ++i) v[i] = __half2float(src[i]);
       }
     }
-    store16(out + 1ll * n * K + k0, v, vec ? 16 : valid);
+    store16(out + 1ll * n * K + k0, v, valid, vec);
   }
 }
 

@@ -87,6 +87,7 @@ struct GemmSmem {
   uint64_t full[4];
   uint64_t empty[4];
   uint64_t accum;
+  uint64_t never;  // nothing ever arrives here (time-out self-test)
   uint32_t tmem_base;
   int abort_flag;
   int row_perm[kMaxBN];       // permuted row of tile row j, or -1

@@ -3,7 +3,9 @@ namespace rdq {
 
 namespace {
 
-__device__ int g_gemm_aborts;  // launches that hit a bounded-wait timeout (diagnostic counter)
+// Status word of the GEMM on this device: 0, or 1 once a CTA gave up a bounded wait (2: the
+// time-out self-test).  Read and cleared by gemm_status().
+__device__ int g_gemm_status;
 
 #ifdef RDQ_GEMM_TIMELINE
 // debug build: per-k-block clocks of CTA (1, 1): [kb][0] MMA warp starts waiting, [1] stage full,
@@ -189,6 +191,7 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
       mbar_init(smem_u32(&S.empty[i]), 1);
     }
     mbar_init(smem_u32(&S.accum), 1);
+    mbar_init(smem_u32(&S.never), 1);
     S.abort_flag = 0;
     mbar_init_fence();
   }
@@ -380,7 +383,12 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kCols)
                  : "memory");
   }
-  if (tid == 0 && S.abort_flag) atomicAdd(&g_gemm_aborts, 1);
+  if (tid == 0 && S.abort_flag) atomicExch(&g_gemm_status, 1);
+  if (a.test_timeout && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    // Self-test of the time-out path: the tile is finished and nothing of this CTA is in flight;
+    // wait (three suspended tries) on a barrier that nothing completes and report it.
+    if (!mbar_wait(smem_u32(&S.never), 0, 3u)) atomicExch(&g_gemm_status, 2);
+  }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -404,12 +412,12 @@ __global__ void __launch_bounds__(256) gemm_reduce_kernel(const GemmArgs a, int 
 template <int MT, int BN>
 int launch_cfg(const CUtensorMap &xmap, const GemmArgs &a, int N, cudaStream_t stream) {
   using Cfg = GemmCfg<MT, BN>;
-  static bool attr_done[64] = {};
+  static std::atomic<bool> attr_done[64];
   int dev = 0;
   RDQ_CUDA(cudaGetDevice(&dev));
-  if (dev < 64 && !attr_done[dev]) {
+  if (dev < 0 || dev >= 64 || !attr_done[dev].load()) {
     RDQ_CUDA(cudaFuncSetAttribute(gemm_mixed_kernel<MT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
-    attr_done[dev] = true;
+    if (dev >= 0 && dev < 64) attr_done[dev].store(true);
   }
   const dim3 grid((a.M + MT * BM - 1) / (MT * BM), (N + BN - 1) / BN, a.ksplit);
   gemm_mixed_kernel<MT, BN><<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(xmap, a);
@@ -470,14 +478,36 @@ extern "C" int rdq_debug_gemm_timeline(long long *host_out) {
 }
 #endif
 
+namespace {
+std::atomic<int> g_gemm_test_timeout{0};
+}
+
+void gemm_set_test_timeout(bool on) { g_gemm_test_timeout.store(on ? 1 : 0); }
+
+int gemm_status(bool reset, cudaStream_t stream) {
+  int code = 0;
+  RDQ_CUDA(cudaMemcpyFromSymbolAsync(&code, g_gemm_status, sizeof(code), 0, cudaMemcpyDeviceToHost, stream));
+  RDQ_CUDA(cudaStreamSynchronize(stream));
+  if (reset && code != 0) {
+    const int zero = 0;
+    RDQ_CUDA(cudaMemcpyToSymbolAsync(g_gemm_status, &zero, sizeof(zero), 0, cudaMemcpyHostToDevice, stream));
+    RDQ_CUDA(cudaStreamSynchronize(stream));
+  }
+  RDQ_REQUIRE(code == 0, RDQ_E_DEVICE, "prefill GEMM: a bounded device-side wait ran out (status %d%s); results of that launch are invalid",
+              code, code == 2 ? ": time-out self-test" : "");
+  return RDQ_OK;
+}
+
 int launch_gemm(const GemmArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
-  static EncodeTiledFn encode = nullptr;
+  static std::atomic<EncodeTiledFn> encode_cached{nullptr};
+  EncodeTiledFn encode = encode_cached.load();
   if (!encode) {
     cudaDriverEntryPointQueryResult qr;
     void *fn = nullptr;
     RDQ_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr));
     RDQ_REQUIRE(fn != nullptr && qr == cudaDriverEntryPointSuccess, RDQ_E_CUDA, "cuTensorMapEncodeTiled is not available");
     encode = reinterpret_cast<EncodeTiledFn>(fn);
+    encode_cached.store(encode);
   }
   const int N = a.n4 + a.n8 + a.n16;
   CUtensorMap xmap;
@@ -494,6 +524,7 @@ int launch_gemm(const GemmArgs &a, void *workspace, size_t workspace_bytes, cuda
   const GemmPlan plan = gemm_plan(a.M, N, a.K);
   b.ksplit = 1;
   b.partial = nullptr;
+  b.test_timeout = g_gemm_test_timeout.load();
   if (plan.ksplit > 1 && workspace != nullptr && workspace_bytes >= sizeof(float) * plan.ksplit * a.M * N) {
     b.ksplit = plan.ksplit;
     b.partial = static_cast<float *>(workspace);

@@ -65,10 +65,7 @@ constexpr int kThreads = (kMmaWarps + 1 + kEpiWarps) * 32;  // + producer warp +
 constexpr int kFlushRing = 2;  // slots of a hand-over ring (one per warp group and epilogue warp)
 constexpr int kMetaSegs = 16;       // tiles per CTA whose output metadata is preloaded into shared memory
 constexpr int kMaxStages = 12;
-#ifndef RDQ_CHUNK_MAX
-#define RDQ_CHUNK_MAX 2048
-#endif
-constexpr int kChunkMax = RDQ_CHUNK_MAX;  // longest k chunk of an image, in NVFP4 elements
+constexpr int kChunkMax = 2048;  // longest k chunk of an image, in NVFP4 elements
 constexpr int kMaxList = 256;       // images one CTA can stream (stage list entries)
 
 // pitch of a block-scale row inside an NVFP4 image: the payload (ck / 16 bytes) rounded up to
@@ -96,8 +93,13 @@ int tiled_chunk_k(int K) {
 }
 
 bool tiled_supported(int n4, int n8, int n16, int K) {
-  if (tiled_chunk_k(K) == 0) return false;
+  const int ck = tiled_chunk_k(K);
+  if (ck == 0) return false;
   if ((n4 % kTileRows) || (n8 % kTileRows) || (n16 % kTileRows)) return false;
+  // a stage-list entry holds the chunk index of an image inside its tile in 8 bits: awkward K
+  // (short chunks) with more images per tile than that run on the any-shape kernel
+  const int s4 = K / ck;
+  if ((n16 > 0 && 4 * s4 > 256) || (n8 > 0 && 2 * s4 > 256) || (n4 > 0 && s4 > 256)) return false;
   return n4 + n8 + n16 > 0;
 }
 

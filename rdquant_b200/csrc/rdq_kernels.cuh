@@ -2,6 +2,11 @@
 // kernel translation units.
 #pragma once
 
+#include <algorithm>
+#include <atomic>
+#include <cstdlib>
+#include <mutex>
+
 #include "rdq_common.cuh"
 
 namespace rdq {
@@ -20,8 +25,8 @@ struct GemvArgs {
   const __half *bias;
   __half *y;
   int n4, n8, n16, K;
-  float *workspace;   // stream kernel: per-CTA partial-tile slots
-  int32_t *counters;  // stream kernel: per-tile arrival counters + status word
+  float *workspace;   // unused by the any-shape kernel
+  int32_t *counters;
 };
 
 struct GemmArgs {
@@ -39,6 +44,7 @@ struct GemmArgs {
   int n4, n8, n16, K;
   int ksplit;      // CTAs that share the k range of a tile (blockIdx.z); 1 = no split
   float *partial;  // ksplit > 1: raw FP32 sums [ksplit][M][N], reduced by a second kernel
+  int test_timeout = 0;  // self-test: CTA (0,0,0) ends with a wait that runs out
 };
 
 int launch_dequant(const void *w_fp4, const void *w_fp4_scales, float global4, const void *w_fp8,
@@ -47,12 +53,6 @@ int launch_dequant(const void *w_fp4, const void *w_fp4_scales, float global4, c
                    int K, cudaStream_t stream);
 
 int launch_gemv_generic(const GemvArgs &a, cudaStream_t stream);
-
-// True when the TMA-staged stream kernel accepts the shape / pointers.
-bool gemv_stream_supported(const GemvArgs &a);
-int launch_gemv_stream(const GemvArgs &a, bool pdl, bool l2_prefetch_on, cudaStream_t stream);
-// workspace floats / counter ints the stream kernel needs for N output rows
-void gemv_stream_scratch(int N, size_t *workspace_bytes, size_t *counter_bytes);
 
 // ---- tiled layout (rdq_gemv_tiled.cu)
 struct GemvTiledArgs {
@@ -67,6 +67,7 @@ struct GemvTiledArgs {
   int n4, n8, n16, K;
   float *workspace;
   int32_t *flags;
+  int test_timeout = 0;  // RDQ_GEMV_TEST_TIMEOUT
 };
 int tiled_chunk_k(int K);
 bool tiled_supported(int n4, int n8, int n16, int K);
@@ -77,8 +78,15 @@ void gemv_tiled_scratch(size_t *workspace_bytes, size_t *flag_bytes);
 int launch_gemv_tiled(const GemvTiledArgs &a, bool pdl, cudaStream_t stream);
 // same kernel with the scratch in a library-owned device array (no allocation anywhere)
 int gemv_tiled_noalloc(const GemvTiledArgs &a, bool pdl, cudaStream_t stream);
+// synchronise `stream`, report (and optionally clear) the kernel's status word; null scratch
+// pointers select the library array of the no-allocation entry point
+int gemv_tiled_status(float *workspace, int32_t *flags, bool reset, cudaStream_t stream);
 
 int launch_gemm(const GemmArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+// synchronise `stream`, report (and optionally clear) the GEMM's per-device status word
+int gemm_status(bool reset, cudaStream_t stream);
+// self-test switch: launches made while it is on end with a wait that runs out
+void gemm_set_test_timeout(bool on);
 size_t gemm_workspace_bytes(int M, int N, int K);
 
 // staging copy by kernel (rdq_stage.cu)

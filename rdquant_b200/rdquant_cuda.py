@@ -8,6 +8,7 @@ surface as ``RuntimeError`` like the reference's ``TORCH_CHECK``s.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -15,7 +16,9 @@ import torch
 from rdquant_b200 import _lib
 
 MAX_GEMV_M = 16
-GEMM_READY = True
+# RDQ_B200_VALIDATE=1: synchronise after every GEMV / GEMM call and raise if the kernel gave up a
+# bounded device-side wait (debugging aid; costs a device round trip per call)
+VALIDATE = os.environ.get("RDQ_B200_VALIDATE", "0") not in ("", "0")
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -75,6 +78,26 @@ def gemv_scratch(n_out: int, device) -> tuple[torch.Tensor, torch.Tensor]:
     workspace = torch.full((max(ws.value // 4, 1),), -1, dtype=torch.int32, device=device).view(torch.float32)
     counters = torch.zeros(max(cnt.value // 4, 1), dtype=torch.int32, device=device)
     return workspace, counters
+
+
+def check_status(fd: dict) -> None:
+    """Wait for the work queued on the current stream and raise ``RuntimeError`` if a tiled-GEMV
+    launch on this layer's scratch gave up a bounded wait (its output is then invalid).  The
+    scratch is put back to its idle state in that case, so the layer stays usable."""
+    ws, cnt = fd.get("workspace"), fd.get("tile_counters")
+    if ws is None or cnt is None:
+        return
+    with _on_device(ws.device):
+        rc = _lib.lib().rdq_gemv_tiled_status(_ptr(ws), _ptr(cnt), 1, _stream(ws.device))
+    _lib.check(rc, "rdq_gemv_tiled_status")
+
+
+def check_gemm_status(device) -> None:
+    """The same for the prefill GEMM (one status word per device, cleared when it is reported)."""
+    device = torch.device(device)
+    with _on_device(device):
+        rc = _lib.lib().rdq_gemm_status(1, _stream(device))
+    _lib.check(rc, "rdq_gemm_status")
 
 
 def dequantize_packed(layer_data: dict, splits: dict, k: int, inv_perm: Optional[torch.Tensor] = None,
@@ -170,6 +193,8 @@ def mixed_gemv(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None, f
                 _ptr(fd.get("perm")), _ptr(bias), _ptr(y), n4, n8, n16, k, _ptr(fd.get("workspace")),
                 _ptr(fd.get("tile_counters")), int(flags), _stream(x.device))
         _lib.check(rc, "rdq_gemv_tiled")
+        if VALIDATE:
+            check_status(fd)
         return y
     with _on_device(x.device):
         rc = _lib.lib().rdq_gemv_mixed(
@@ -215,6 +240,8 @@ def mixed_gemm(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None) -
             _ptr(fd.get("w_fp8_q")), _ptr(fd.get("w_fp8_scales")), _ptr(fd.get("w_fp16")), _ptr(fd.get("inv_perm")),
             _ptr(bias), _ptr(y), n4, n8, n16, k, _ptr(ws), need.value, _stream(x.device))
     _lib.check(rc, "rdq_gemm_mixed")
+    if VALIDATE:
+        check_gemm_status(x.device)
     return y
 
 
@@ -222,9 +249,10 @@ def mixed_linear(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None,
     """GEMV for M <= 16, GEMM above."""
     if x.shape[0] <= MAX_GEMV_M:
         return mixed_gemv(x, fd, bias, flags)
-    if GEMM_READY:
+    if fd["k"] % 64 == 0:
         return mixed_gemm(x, fd, bias)
-    # until the tensor-core GEMM is enabled: the decode kernel over 16-row panels
+    # the tensor-core GEMM tiles K in blocks of 64; other K run the decode kernel over 16-row
+    # panels (the reference's dense prefill takes any K, rdquant/inference.py:679-687)
     n = fd["n_fp4"] + fd["n_fp8"] + fd["n_fp16"]
     y = torch.empty(x.shape[0], n, dtype=torch.float16, device=x.device)
     for r0 in range(0, x.shape[0], MAX_GEMV_M):

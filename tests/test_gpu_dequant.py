@@ -62,7 +62,10 @@ def test_golden_layers_bit_exact(layers):
         assert np.array_equal(w32.cpu().numpy().view(np.uint32), case["w_ref_f32"].view(np.uint32)), name
 
 
-@pytest.mark.parametrize("n4,n8,n16,k", [(128, 128, 128, 2560), (48, 16, 0, 64), (0, 33, 7, 40), (640, 256, 128, 256)])
+# K = 20 and 36 (no NVFP4 group) give rows whose 16-element runs are not 16-byte aligned in the
+# f16 (K % 8 != 0) and f32 (K % 4 == 0 but full runs start at odd multiples of 16 B) outputs
+@pytest.mark.parametrize("n4,n8,n16,k", [(128, 128, 128, 2560), (48, 16, 0, 64), (0, 33, 7, 40), (640, 256, 128, 256),
+                                         (0, 19, 5, 20), (0, 9, 12, 36), (0, 0, 3, 17)])
 def test_random_bytes_vs_oracle(n4, n8, n16, k):
     layer = random_packed_layer(n4, n8, n16, k, seed=n4 + k)
     splits = dict(zip(ORDER, (n4, n8, n16)))
@@ -70,6 +73,9 @@ def test_random_bytes_vs_oracle(n4, n8, n16, k):
     dev = {kk: v.cuda() for kk, v in layer.items()}
     w = rdquant_cuda.dequantize_packed(dev, splits, k, inv_perm=dev["inv_permutation"])
     assert np.array_equal(_bits16(w), ref.view(np.uint16))
+    w32 = rdquant_cuda.dequantize_packed(dev, splits, k, inv_perm=dev["inv_permutation"], out_dtype=torch.float32)
+    ref32 = onp.dequantize_layer_f32(onp.torch_layer_to_np(layer), splits, k)
+    assert np.array_equal(w32.cpu().numpy().view(np.uint32), ref32.view(np.uint32))
 
 
 def test_formats_dequantize_and_qweight(layers):

@@ -40,12 +40,12 @@ def test_golden_layers(layers, flags):
 
 @pytest.mark.parametrize("m", [1, 2, 4, 8, 9, 16])
 @pytest.mark.parametrize("shape", [(128, 128, 128, 256), (64, 32, 16, 512), (256, 0, 0, 1024), (0, 48, 0, 256),
-                                   (0, 0, 32, 768), (1664, 768, 128, 4096), (48, 32, 16, 1216), (16, 16, 16, 4160)])
-@pytest.mark.parametrize("flags", [_lib.RDQ_GEMV_GENERIC, _lib.RDQ_GEMV_STREAM, _lib.RDQ_GEMV_AUTO])
+                                   (0, 0, 32, 768), (1664, 768, 128, 4096), (48, 32, 16, 1216), (16, 16, 16, 4160),
+                                   (64, 0, 0, 256), (0, 64, 0, 512), (0, 0, 64, 256), (192, 64, 64, 768),
+                                   (64, 64, 64, 9728)])
+@pytest.mark.parametrize("flags", [_lib.RDQ_GEMV_GENERIC, _lib.RDQ_GEMV_AUTO])
 def test_random_bytes(shape, m, flags):
     n4, n8, n16, k = shape
-    if flags == _lib.RDQ_GEMV_STREAM and k % 256:
-        pytest.skip("row-major stream kernel needs K % 256 == 0")
     layer = random_packed_layer(n4, n8, n16, k, seed=k + m)
     splits = dict(zip(ORDER, (n4, n8, n16)))
     y, y_ref, _ = _run(layer, splits, k, m, flags, bias=(m % 2 == 0), seed=m)
@@ -54,8 +54,8 @@ def test_random_bytes(shape, m, flags):
 
 @pytest.mark.parametrize("m", [1, 5, 16])
 def test_many_tiles_per_cta(m):
-    """Short rows, many channels: every CTA finishes more than 32 tiles (the segment table is
-    built in several chunks, the hand-over rings wrap many times)."""
+    """Short rows, many channels: every warp group finishes several whole tiles and its ring
+    wraps."""
     n4, n8, n16, k = 60800, 20480, 5120, 256
     layer = random_packed_layer(n4, n8, n16, k, seed=11)
     splits = dict(zip(ORDER, (n4, n8, n16)))
@@ -69,8 +69,24 @@ def test_ragged_shapes_take_generic_kernel():
         splits = dict(zip(ORDER, (n4, n8, n16)))
         y, y_ref, _ = _run(layer, splits, k, 3, _lib.RDQ_GEMV_AUTO)
         assert onp.rel_err(y, y_ref) < TOL
-        with pytest.raises(RuntimeError):
-            _run(layer, splits, k, 1, _lib.RDQ_GEMV_STREAM)
+
+
+def test_tiled_layout_predicate():
+    """Which shapes get the tiled layout (groups in multiples of 16 rows, K divisible into chunks
+    that are multiples of 64, at most 256 chunks per tile); everything else -- here K = 4288 =
+    64 x 67, whose FP16 tiles would have 268 chunks -- runs the any-shape kernel and must still
+    match the oracle."""
+    lib = _lib.lib()
+    assert lib.rdq_gemv_tiled_bytes(128, 64, 64, 512) > 0
+    assert lib.rdq_gemv_tiled_bytes(16, 16, 0, 4288) > 0      # 67 / 134 chunks per tile: fine
+    for shape in [(16, 16, 16, 4288), (0, 0, 16, 4288), (10, 0, 0, 256), (16, 0, 0, 100)]:
+        assert lib.rdq_gemv_tiled_bytes(*shape) == 0
+    n4, n8, n16, k = 16, 16, 16, 4288
+    layer = random_packed_layer(n4, n8, n16, k, seed=9)
+    splits = dict(zip(ORDER, (n4, n8, n16)))
+    y, y_ref, fd = _run(layer, splits, k, 2, _lib.RDQ_GEMV_AUTO)
+    assert fd["w_tiled"] is None
+    assert onp.rel_err(y, y_ref) < TOL
 
 
 @pytest.mark.parametrize("name", list(QWEN3_4B_BLOCK))
@@ -105,3 +121,32 @@ def test_reference_signature_entry_point():
     with pytest.raises(RuntimeError):
         rdquant_cuda.fused_mixed_gemv(x.cuda().float(), dev["weight_nvfp4"], dev["weight_nvfp4_scale"], 1.0,
                                       dev["weight_fp8"], dev["weight_fp8_scale"], dev["inv_permutation"], n4, n8, k)
+
+
+@pytest.mark.parametrize("m", [1, 4, 8, 16])
+@pytest.mark.parametrize("group", [["q_proj", "k_proj", "v_proj"], ["gate_proj", "up_proj"]])
+def test_fused_sibling_projections(group, m):
+    """The layers the benchmark times: q+k+v (2560 -> 6144) and gate+up (2560 -> 19456) packed as
+    one layer each by fuse_layers, PDL launch flag on, against the oracle on every member layer."""
+    from rdquant_b200.fused_gemv_pack import fuse_layers
+
+    members = []
+    for i, name in enumerate(group):
+        k, n = QWEN3_4B_BLOCK[name]
+        splits = fixed_splits(n)
+        members.append((random_packed_layer(splits["NVFP4"], splits["FP8"], splits["FP16"], k, seed=31 + i + m), splits))
+    k = QWEN3_4B_BLOCK[group[0]][0]
+    data, splits = fuse_layers(members)
+    fd = pack_for_fused_gemv(data, splits, k, "cuda")
+    assert fd["w_tiled"] is not None
+    x = torch.randn(m, k, generator=torch.Generator().manual_seed(m)).half()
+    y = rdquant_cuda.mixed_gemv(x.cuda(), fd, None, _lib.RDQ_GEMV_PDL)
+    rdquant_cuda.check_status(fd)
+    y = y.cpu().float().numpy()
+    off = 0
+    for layer, sp in members:
+        n = sum(sp.values())
+        y_ref = onp.mixed_precision_linear(x.numpy(), onp.torch_layer_to_np(layer), sp, k)
+        assert onp.rel_err(y[:, off:off + n], y_ref) < TOL, (group, m, off)
+        off += n
+    assert off == y.shape[1]

@@ -41,6 +41,7 @@ def test_no_alloc_entry_matches_scratch_entry(shape, m):
         err = (y.float() - y_ref.float()).abs().max() / y_ref.float().abs().max()
         assert float(err) < TOL, (call, float(err))
         assert torch.equal(y, y_ref), f"call {call}: not the same bits as the scratch entry point"
+        assert lib.rdq_gemv_tiled_noalloc_status(0, stream) == 0, lib.rdq_last_error()
 
 
 def test_no_alloc_entry_rejects_bad_shapes():
@@ -49,3 +50,31 @@ def test_no_alloc_entry_rejects_bad_shapes():
     assert rc == -2 and b"activation rows" in lib.rdq_last_error()
     rc = lib.rdq_gemv_tiled_noalloc(None, 1, None, None, 1.0, None, None, None, 10, 0, 0, 256, 0, None)
     assert rc == -2 and b"tiled layout" in lib.rdq_last_error()
+
+
+def test_no_alloc_entry_reports_and_clears_a_timeout():
+    """The status word of the built-in array is readable and the array can be put back to idle:
+    a launch that gave up a wait (here the self-test wait on a barrier nothing completes) must
+    not poison the calls that follow."""
+    n4, n8, n16, k = 256, 128, 64, 1024
+    splits = dict(zip(ORDER, (n4, n8, n16)))
+    fd = pack_for_fused_gemv(random_packed_layer(n4, n8, n16, k, seed=22), splits, k, "cuda")
+    x = torch.randn(1, k, generator=torch.Generator().manual_seed(7)).half().cuda()
+    y_ref = rdquant_cuda.mixed_gemv(x, fd)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    lib = _lib.lib()
+
+    def call(flags):
+        y = torch.zeros_like(y_ref)
+        rc = lib.rdq_gemv_tiled_noalloc(_p(x), 1, _p(fd["w_tiled"]), _p(fd["w_fp8_scales"]), 1.0, _p(fd["perm"]),
+                                        None, _p(y), n4, n8, n16, k, flags, stream)
+        assert rc == 0, lib.rdq_last_error()
+        return y
+
+    call(_lib.RDQ_GEMV_TEST_TIMEOUT)
+    assert lib.rdq_gemv_tiled_noalloc_status(1, stream) == _lib.RDQ_E_DEVICE
+    assert b"status 9" in lib.rdq_last_error()
+    assert lib.rdq_gemv_tiled_noalloc_status(0, stream) == 0
+    y = call(0)
+    assert lib.rdq_gemv_tiled_noalloc_status(0, stream) == 0
+    assert torch.equal(y, y_ref)
