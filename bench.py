@@ -1,22 +1,31 @@
 #!/usr/bin/env python
-"""Benchmark of the mixed-precision decode GEMV on the Qwen3-4B-shaped decoder block.
+"""Benchmark of the mixed-precision linear operator on the Qwen3-4B-shaped decoder block.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--m M] [--impl ours|reference]
 
-A "step" is one pass over the seven linears of one decoder block (q, k, v, o, gate, up,
-down; 67/32/1 NVFP4/FP8/FP16 split rounded to 128 channels, random channel permutation,
-seeded synthetic weights ~ N(0, 0.02) with 1 % outlier channels x8) at M activation rows:
-seven PDL-chained GEMV launches.  The metric is packed weight + scale bytes streamed per
-second (GB/s).  Weight copies rotate through more than twice the L2 capacity, so every
-launch reads HBM.  With N > 1 (torchrun) every rank streams its own block-sized shard; no
-collective is on this path.
+A "step" is one pass over the seven linears of one decoder block (q, k, v, o, gate, up, down;
+67/32/1 NVFP4/FP8/FP16 split rounded to 128 channels, random channel permutation, seeded
+synthetic weights ~ N(0, 0.02) with 1 % outlier channels x8) at M activation rows through the
+decode GEMV: four PDL-chained launches (q/k/v and gate/up read the same input and are packed as
+one layer each).  The metric is packed weight + scale bytes streamed per second (GB/s).  Weight
+copies rotate through more than twice the L2 capacity, so every launch reads HBM.
 
-Prints ONE JSON line (rank 0).  `--impl reference` times the CPU restatement of the
-reference operator (oracle/rdq_oracle.c, all host threads) on a bounded sample.
+N = 1 also reports, in the same JSON line, the tcgen05 prefill GEMM on the same block
+(`prefill`: TFLOP/s at 512 / 2048 / 8192 tokens beside cuBLAS dense f16 on the same shapes, which
+is what the reference's prefill runs) and whole-model greedy decoding of the 36-layer
+Qwen3-4B-shaped stack (`decode`: tokens/s).
+
+N > 1 (torchrun): ONE block is cut column-parallel at 128-channel boundaries of every format
+group (rdquant_b200.parallel); every rank streams its rows, and the per-layer NCCL all-gather and
+un-permute are inside the timed CUDA graph ("strong" scaling: value = the block's bytes / step).
+
+Prints ONE JSON line (rank 0).  `--impl reference` times the CPU restatement of the reference
+operator (oracle/rdq_oracle.c, all host threads) on a bounded sample of the same block.
 """
 import argparse
 import json
 import os
+import statistics
 import subprocess
 import sys
 import threading
@@ -29,6 +38,9 @@ if ROOT not in sys.path:
 METRIC = "mixed_gemv_hbm_gbps"
 UNIT = "GB/s"
 LAYER_ORDER = ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"]
+FUSE_GROUPS = [["q_proj", "k_proj", "v_proj"], ["o_proj"], ["gate_proj", "up_proj"], ["down_proj"]]
+L2_BYTES = 126e6
+TOL = 2e-3
 
 
 def measured_peaks():
@@ -37,6 +49,17 @@ def measured_peaks():
         with open(path) as fh:
             return json.load(fh), "measured"
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+def profiled_traffic(kernel: str, workload: str):
+    """dram bytes per launch of the dominant kernel from the tracked ncu summary data
+    (profiles/traffic.json), or None when no capture of this kernel / workload is on file."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        with open(path) as fh:
+            return json.load(fh).get(kernel, {}).get(workload)
+    except (OSError, ValueError):
+        return None
 
 
 class ClockSampler:
@@ -95,15 +118,12 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-FUSE_GROUPS = [["q_proj", "k_proj", "v_proj"], ["o_proj"], ["gate_proj", "up_proj"], ["down_proj"]]
-
-
-def build_block(device, seed: int, copies: int, fuse: bool):
-    """`copies` independent device copies of the packed linears of one block.  With `fuse`,
-    projections that read the same input (q/k/v, gate/up) are packed as one layer each."""
+def block_layers(device, seed: int):
+    """Packed checkpoint tensors (on `device`) of the seven linears of one block:
+    {name: (layer_data, splits, k, n)}."""
     import torch
 
-    from rdquant_b200.fused_gemv_pack import fuse_layers, layer_data_from_qweight, pack_for_fused_gemv, packed_weight_bytes
+    from rdquant_b200.fused_gemv_pack import layer_data_from_qweight
     from rdquant_b200.quantize import quantize_weight
     from rdquant_b200.synthetic import QWEN3_4B_BLOCK, fixed_splits, synthetic_weight
 
@@ -118,6 +138,13 @@ def build_block(device, seed: int, copies: int, fuse: bool):
         qw = quantize_weight(w.to(device).float(), perm.to(device), splits)
         per_layer[name] = (layer_data_from_qweight(qw), splits, k, n)
         del w, qw
+    return per_layer
+
+
+def fused_units(per_layer, fuse: bool):
+    """[(name, layer_data, splits, k, n, bytes, members)] of the launches of a step."""
+    from rdquant_b200.fused_gemv_pack import fuse_layers, packed_weight_bytes
+
     groups = FUSE_GROUPS if fuse else [[n] for n in LAYER_ORDER]
     units = []
     for group in groups:
@@ -127,15 +154,41 @@ def build_block(device, seed: int, copies: int, fuse: bool):
             data, splits = fuse_layers([(per_layer[g][0], per_layer[g][1]) for g in group])
         else:
             data, splits = per_layer[group[0]][0], per_layer[group[0]][1]
-        fds = [pack_for_fused_gemv({kk: v.clone() for kk, v in data.items()}, splits, k, device) for _ in range(copies)]
-        units.append({"name": "+".join(group), "k": k, "n": sum(per_layer[g][3] for g in group), "splits": splits,
-                      "fds": fds, "bytes": nbytes})
+        units.append({"name": "+".join(group), "data": data, "splits": splits, "k": k,
+                      "n": sum(per_layer[g][3] for g in group), "bytes": nbytes, "members": group})
     return units
+
+
+def build_block(device, seed: int, copies: int, fuse: bool):
+    """`copies` independent device copies of the packed linears of one block.  With `fuse`,
+    projections that read the same input (q/k/v, gate/up) are packed as one layer each."""
+    from rdquant_b200.fused_gemv_pack import pack_for_fused_gemv
+
+    per_layer = block_layers(device, seed)
+    units = fused_units(per_layer, fuse)
+    for u in units:
+        u["fds"] = [pack_for_fused_gemv({kk: v.clone() for kk, v in u["data"].items()}, u["splits"], u["k"], device)
+                    for _ in range(copies)]
+    return units, per_layer
+
+
+def oracle_outputs(per_layer, unit, x_f16):
+    """CPU oracle output [M, n] of one (possibly fused) launch: the member layers side by side."""
+    import numpy as np
+
+    from oracle import oracle_np as onp
+
+    parts = []
+    for name in unit["members"]:
+        data, splits, k, _ = per_layer[name]
+        layer = onp.torch_layer_to_np({kk: v.cpu() for kk, v in data.items()})
+        parts.append(onp.mixed_precision_linear(x_f16, layer, splits, k))
+    return np.concatenate(parts, axis=1)
 
 
 def cpu_baseline(budget_s: float = 12.0) -> dict:
     """The CPU restatement of the reference operator (re-dequantises per call, like
-    rdquant/ops.py:55-60) on gate_proj (2560 -> 9728) at M = 1, all host threads."""
+    rdquant/ops.py:55-60) on the seven linears of the block at M = 1, all host threads."""
     import numpy as np
     import torch
 
@@ -146,96 +199,327 @@ def cpu_baseline(budget_s: float = 12.0) -> dict:
 
     oracle_c.build()
     oracle_c.set_threads(os.cpu_count() or 1)  # launchers like torchrun export OMP_NUM_THREADS=1
-    k, n = QWEN3_4B_BLOCK["gate_proj"]
-    gen = torch.Generator().manual_seed(4)
-    w = synthetic_weight(n, k, gen)
-    perm = torch.randperm(n, generator=gen)
-    splits = fixed_splits(n)
-    qw = quantize_weight(w.float(), perm, splits)
-    q4, q8, q16 = qw.qtensors["NVFP4"], qw.qtensors["FP8"], qw.qtensors["FP16"]
-    args = (np.ascontiguousarray(q4.data.numpy()), np.ascontiguousarray(q4.scales.numpy()), splits["NVFP4"],
-            np.ascontiguousarray(q8.data.numpy()), float(q8.scales.item()), splits["FP8"],
-            np.ascontiguousarray(q16.data.numpy()), splits["FP16"], qw.inv_permutation.numpy())
-    x = torch.randn(1, k, generator=gen).half().numpy()
-    oracle_c.linear(x, *args)
-    calls, t0 = 0, time.perf_counter()
+    calls_args, nbytes = [], 0
+    for li, name in enumerate(LAYER_ORDER):
+        k, n = QWEN3_4B_BLOCK[name]
+        gen = torch.Generator().manual_seed(400 + li)
+        w = synthetic_weight(n, k, gen)
+        perm = torch.randperm(n, generator=gen)
+        splits = fixed_splits(n)
+        qw = quantize_weight(w.float(), perm, splits)
+        q4, q8, q16 = qw.qtensors["NVFP4"], qw.qtensors["FP8"], qw.qtensors["FP16"]
+        x = torch.randn(1, k, generator=gen).half().numpy()
+        calls_args.append((x, np.ascontiguousarray(q4.data.numpy()), np.ascontiguousarray(q4.scales.numpy()),
+                           splits["NVFP4"], np.ascontiguousarray(q8.data.numpy()), float(q8.scales.item()),
+                           splits["FP8"], np.ascontiguousarray(q16.data.numpy()), splits["FP16"],
+                           qw.inv_permutation.numpy()))
+        nbytes += packed_weight_bytes(splits, k)
+    for a in calls_args:
+        oracle_c.linear(*a)
+    steps, t0 = 0, time.perf_counter()
     while True:
-        oracle_c.linear(x, *args)
-        calls += 1
+        for a in calls_args:
+            oracle_c.linear(*a)
+        steps += 1
         dt = time.perf_counter() - t0
-        if dt > budget_s or calls >= 400:
+        if dt > budget_s or steps >= 200:
             break
-    nbytes = packed_weight_bytes(splits, k)
-    return {"value": nbytes * calls / dt / 1e9, "unit": UNIT, "cores": oracle_c.threads(), "kind": "port",
-            "sample": f"gate_proj 2560->9728, M=1, {calls} calls in {dt:.1f} s ({1e3 * dt / calls:.2f} ms/call)",
-            "ms_per_call": 1e3 * dt / calls, "calls": calls, "bytes_per_call": nbytes}
+    return {"value": nbytes * steps / dt / 1e9, "unit": UNIT, "cores": oracle_c.threads(), "kind": "port",
+            "sample": f"all 7 linears of the block, M=1, {steps} block passes in {dt:.1f} s "
+                      f"({1e3 * dt / steps:.1f} ms/pass)",
+            "ms_per_step": 1e3 * dt / steps, "steps": steps, "bytes_per_step": nbytes}
 
 
 def run_reference(args, rank: int, world: int) -> None:
     if rank != 0:
         return
-    steps = max(args.steps, 1)
-    base = cpu_baseline(budget_s=min(60.0, 0.25 * (steps + args.warmup) + 8.0))
+    base = cpu_baseline(budget_s=min(60.0, 0.25 * (max(args.steps, 1) + args.warmup) + 8.0))
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_call"], "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16xf16->f32", "data": "synthetic",
-        "config": {"workload": "qwen3-4b decoder block, 7 mixed-precision linears, M=1 decode GEMV",
-                   "sample": base["sample"], "note": "reference is a Python package; timed here as its C restatement "
-                   "(oracle/rdq_oracle.c) on the host cores"},
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "f16xf16->f32", "data": "synthetic",
+        "config": {"workload": "qwen3-4b decoder block: q,k,v,o,gate,up,down mixed-precision linears, M=1 decode GEMV",
+                   "sample": base["sample"], "note": "the reference operator is a Python package that cannot travel to "
+                   "the GPU box; timed here as its C restatement (oracle/rdq_oracle.c) on the host cores, "
+                   "re-dequantising per call like rdquant/ops.py:55-60"},
         "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-def run_prefill(args, device, rank: int, world: int) -> None:
-    """Prefill GEMM (BASELINE configs[2]): the seven linears of the block at `--prefill` tokens."""
+def time_replays(graph, stream, replays: int):
+    """Device times (ms) of `replays` replays of a CUDA graph, each bracketed by events."""
+    import torch
+
+    times = []
+    for _ in range(replays):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        graph.replay()
+        e1.record(stream)
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return times
+
+
+def prefill_section(device, units, tokens=(512, 2048, 8192), steps: int = 10) -> dict:
+    """tcgen05 prefill GEMM on the block's four launches at each token count, beside cuBLAS dense
+    f16 (torch F.linear over a materialised weight: the reference's prefill path,
+    rdquant/inference.py:679-687) on the same shapes in the same run."""
     import torch
 
     from rdquant_b200 import rdquant_cuda
 
-    m = args.prefill
-    steps, warmup = max(min(args.steps, 50), 1), max(args.warmup, 3)
-    units = build_block(device, seed=rank, copies=1, fuse=not args.no_fuse)
-    gen = torch.Generator().manual_seed(99 + rank)
-    xs = [torch.randn(m, u["k"], generator=gen).half().to(device) for u in units]
-    flops = sum(2.0 * m * u["n"] * u["k"] for u in units)
+    peaks, _ = measured_peaks()
+    sustained = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+    out = {}
+    dense = [torch.randn(u["n"], u["k"], device=device, dtype=torch.float16) * 0.02 for u in units]
+    for m in tokens:
+        gen = torch.Generator().manual_seed(99 + m)
+        xs = [torch.randn(m, u["k"], generator=gen).half().to(device) for u in units]
+        flops = sum(2.0 * m * u["n"] * u["k"] for u in units)
+
+        def ours():
+            for x, u in zip(xs, units):
+                rdquant_cuda.mixed_gemm(x, u["fds"][0])
+
+        def cublas():
+            for x, w in zip(xs, dense):
+                torch.nn.functional.linear(x, w)
+
+        res = {}
+        for name, fn in (("tflops", ours), ("cublas_dense_tflops", cublas)):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            e1.synchronize()
+            res[name] = flops * steps / (e0.elapsed_time(e1) * 1e-3) / 1e12
+        rdquant_cuda.check_gemm_status(device)
+        res["frac_sustained"] = res["tflops"] / sustained
+        res["vs_cublas_dense"] = res["tflops"] / res["cublas_dense_tflops"]
+        out[str(m)] = res
+        del xs
+    return out
+
+
+def decode_section(device, batches=(1, 8), prompt: int = 512, new_tokens: int = 256, cfg=None, rank=0, world=1,
+                   gemv_block_ms=None) -> dict:
+    """Whole-model greedy decoding (BASELINE configs[3]): random-init Qwen3-4B-shaped stack, all
+    linears mixed-precision, `prompt`-token prefill through the GEMM, then `new_tokens` tokens, one
+    CUDA-graph replay per token.  tokens/s = batch * new_tokens / device time of the decode loop."""
+    import torch
+    import torch.distributed as dist
+
+    from rdquant_b200.decoder import QWEN3_4B, MixedDecoder
+
+    cfg = cfg or QWEN3_4B
+    out = {"model": cfg.name, "layers": cfg.layers, "prompt_tokens": prompt, "new_tokens": new_tokens, "batch": {}}
+    t_build = time.time()
+    model = MixedDecoder(cfg, device, max_seq=prompt + new_tokens + 8, batch=batches[0], seed=7, rank=rank, world=world)
+    torch.cuda.synchronize()
+    t_build = time.time() - t_build
+    for b in batches:
+        model.reset(b)
+        gen = torch.Generator().manual_seed(11)
+        ids = torch.randint(0, cfg.vocab, (b, prompt), generator=gen).to(device)
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        if world > 1:
+            dist.barrier()
+        e0.record()
+        model.prefill(ids)
+        e1.record()
+        e1.synchronize()
+        model.capture_decode()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e1.record()
+        for _ in range(new_tokens):
+            model.decode_step()
+        e2.record()
+        e2.synchronize()
+        ms_prefill, ms_decode = e0.elapsed_time(e1), e1.elapsed_time(e2)
+        if world > 1:
+            t = torch.tensor([ms_decode], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_decode = float(t[0])
+        res = {"tokens_per_s": b * new_tokens / (ms_decode * 1e-3), "ms_per_token": ms_decode / new_tokens,
+               "prefill_ms": ms_prefill, "linear_bytes": model.linear_bytes, "build_s": round(t_build, 1),
+               "linear_gbps": model.linear_bytes * new_tokens / (ms_decode * 1e-3) / 1e9}
+        if gemv_block_ms is not None and b == 1 and world == 1:
+            # share of a token's time the linears alone would take at the block benchmark's rate
+            res["linear_only_fraction"] = gemv_block_ms * cfg.layers / res["ms_per_token"]
+        out["batch"][str(b)] = res
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_sharded(args, device, rank: int, world: int) -> None:
+    """N > 1: one block, column-parallel; kernel + all-gather + un-permute per layer in the graph."""
+    import torch
+    import torch.distributed as dist
+
+    from rdquant_b200 import rdquant_cuda
+    from rdquant_b200.parallel import ColumnParallelMixedLinear, gather_outputs
+
+    steps, warmup, m = max(args.steps, 1), max(args.warmup, 3), args.m
+    per_layer = block_layers(device, seed=0)  # the same block on every rank
+    units = fused_units(per_layer, fuse=not args.no_fuse)
+    step_bytes = sum(u["bytes"] for u in units)
+    # every rank streams 1/world of the block per step: rotate enough copies to exceed 2 x L2
+    copies = max(args.copies, int(2 * L2_BYTES * world / step_bytes) + 1)
+    mods = [[ColumnParallelMixedLinear({kk: v.clone() for kk, v in u["data"].items()}, u["splits"], u["k"], device,
+                                       rank, world) for u in units] for _ in range(copies)]
+    for row in mods:
+        for mod in row:
+            mod.use_pdl = not args.no_pdl
+    gen = torch.Generator().manual_seed(1234)
+    xs_cpu = [torch.randn(m, u["k"], generator=gen).half() for u in units]
+    xs = [x.to(device) for x in xs_cpu]
+    ys = [None] * len(units)
+
+    def one_step(i: int) -> None:
+        for li, mod in enumerate(mods[i % copies]):
+            ys[li] = mod(xs[li])
+
+    def gathers_only(i: int) -> None:
+        for mod in mods[i % copies]:
+            send, buf, idx = mod._buffers(m)
+            gather_outputs(send, mod.plan, mod.group, buffer=buf, index=idx)
+
     sampler = ClockSampler(device.index or 0)
     sampler.start()
-
-    def one_step():
-        for x, u in zip(xs, units):
-            rdquant_cuda.mixed_gemm(x, u["fds"][0])
-
-    for _ in range(warmup):
-        one_step()
+    for i in range(warmup):
+        one_step(i)
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0 = time.time()
-    e0.record()
-    for _ in range(steps):
-        one_step()
-    e1.record()
-    e1.synchronize()
-    t1 = time.time()
-    ms = e0.elapsed_time(e1)
+    # parity: the gathered outputs of one step against the CPU oracle on the whole layers
+    from oracle import oracle_np as onp
+
+    one_step(0)
+    torch.cuda.synchronize()
+    parity = 0.0
+    if rank == 0:
+        for li, u in enumerate(units):
+            ref = oracle_outputs(per_layer, u, xs_cpu[li].numpy())
+            parity = max(parity, float(onp.rel_err(ys[li].cpu().float().numpy(), ref)))
+    # every rank must hold the same gathered outputs as rank 0
+    for li in range(len(units)):
+        mine = ys[li].float().sum(dtype=torch.float64).reshape(1)
+        lo, hi = mine.clone(), mine.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        if float(hi - lo) != 0.0:
+            raise RuntimeError("ranks disagree on the gathered output of layer %d" % li)
+    for row in mods:
+        for mod in row:
+            rdquant_cuda.check_status(mod.fd)
+
+    stream = torch.cuda.Stream(device)
+    graph, ggraph = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+    replays = 10
+    with torch.cuda.stream(stream):
+        one_step(0)
+        gathers_only(0)
+        stream.synchronize()
+        with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+            for i in range(steps):
+                one_step(i)
+        with torch.cuda.graph(ggraph, stream=stream, capture_error_mode="thread_local"):
+            for i in range(steps):
+                gathers_only(i)
+        t_spin = time.time()
+        while time.time() - t_spin < 0.3:
+            graph.replay()
+            stream.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.time()
+        times = time_replays(graph, stream, replays)
+        t1 = time.time()
+        dist.barrier()
+        gtimes = time_replays(ggraph, stream, 5)
     clocks = sampler.stop(t0, t1)
-    peaks, kind = measured_peaks()
-    tf = flops * steps / (ms * 1e-3) / 1e12
-    sustained = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+
+    # ---- end to end: host activations in, host results out, synchronised every step
+    x_host = [x.clone().pin_memory() for x in xs_cpu]
+    y_host = [torch.zeros(m, u["n"], dtype=torch.float16).pin_memory() for u in units]
+    e2e_steps = min(steps, 200)
+
+    def e2e_step(i: int) -> None:
+        for li, mod in enumerate(mods[i % copies]):
+            xs[li].copy_(x_host[li], non_blocking=True)
+            y_host[li].copy_(mod(xs[li]), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    dist.barrier()
+    te0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    te = time.perf_counter() - te0
+
+    t = torch.tensor([statistics.median(times), min(times), max(times), statistics.median(gtimes), te],
+                     dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_min, ms_max, gms, te = (float(v) for v in t)
+    pt = torch.tensor([parity], dtype=torch.float64, device=device)
+    dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+    parity = float(pt[0])
+    if parity > TOL:
+        raise RuntimeError(f"sharded outputs differ from the oracle: max rel err {parity:.3e} > {TOL}")
+
+    peaks, peak_kind = measured_peaks()
+    launches = steps * len(units)
+    value = step_bytes * steps / (ms * 1e-3) / 1e9
+    per_rank_launch_bytes = step_bytes / world / len(units)
+    achieved = per_rank_launch_bytes / (ms * 1e-3 / launches) / 1e9
     line = {
-        "metric": "mixed_gemm_tflops", "value": tf * world, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
-        "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16xf16->f32", "data": "synthetic",
-        "config": {"workload": f"qwen3-4b decoder block: 7 mixed-precision linears, prefill GEMM at M={m} tokens "
-                               "(BASELINE configs[2])", "launches_per_step": len(units),
-                   "fusion": "q/k/v and gate/up packed as one layer each" if not args.no_fuse else "none", "l2_policy": "activations + outputs of a step exceed L2 for M >= 2048"},
-        "gpu_launches": steps * len(units),
-        "roofline": {"bound": "tensor", "achieved": tf, "peak": sustained, "unit": "TFLOP/s", "frac": tf / sustained,
-                     "traffic": None, "peak_source": kind + " (sustained cuBLAS bf16)", "kernel": "gemm_mixed_kernel"},
+        "config": {
+            "workload": f"qwen3-4b decoder block: q,k,v,o,gate,up,down mixed-precision linears, M={m} decode GEMV",
+            "launches_per_step": len(units),
+            "fusion": "none" if args.no_fuse else "q/k/v and gate/up packed as one layer each (they read the same input)",
+            "split": "67/32/1 NVFP4/FP8/FP16, 128-aligned, random channel permutation",
+            "bytes_per_step": step_bytes,
+            "parallelism": f"column-parallel x{world}: every format group of every layer cut at 128-channel "
+                           "boundaries, x replicated, outputs all-gathered and un-permuted on every rank",
+            "collective": f"all_gather_into_tensor x{len(units)} per step (NCCL, inside the timed CUDA graph)",
+            "l2_policy": f"{copies} rotating weight copies = {copies * step_bytes / world / 1e6:.0f} MB per rank "
+                         "> 2 x L2; no flush",
+            "launch": "one CUDA graph of all timed steps; median of %d replays" % replays,
+            "kernel": "tiled",
+        },
+        "gpu_launches": launches,
+        "timing": {"replays": replays, "ms_per_step_median": ms / steps, "ms_per_step_min": ms_min / steps,
+                   "ms_per_step_max": ms_max / steps},
+        "collective_ms_per_step": gms / steps,
+        "parity_max_rel_err": parity,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peak_kind,
+                     "kernel": "gemv_tiled_kernel", "bytes_per_launch": per_rank_launch_bytes,
+                     "note": "per rank: its share of a launch's bytes over the step time divided by launches; "
+                             "the step time includes the all-gathers"},
+        "e2e": {"value": step_bytes * e2e_steps / te / 1e9, "unit": UNIT,
+                "h2d_bytes_per_step": sum(2 * m * u["k"] for u in units),
+                "d2h_bytes_per_step": sum(2 * m * u["n"] for u in units), "steps": e2e_steps,
+                "ms_per_step": 1e3 * te / e2e_steps,
+                "api": "parallel.ColumnParallelMixedLinear.forward per layer: pinned host x -> device, fused GEMV + "
+                       "all-gather + un-permute, y -> pinned host, synchronised every step"},
         "clocks": clocks,
+        "cpu_baseline": None,
     }
+    if args.decode:
+        line["decode"] = decode_section(device, batches=(1,), rank=rank, world=world)
     if rank == 0:
         print(json.dumps(line), flush=True)
 
@@ -252,8 +536,10 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel", default="tiled", choices=["tiled", "generic"])
     ap.add_argument("--no-fuse", action="store_true", help="seven launches per step instead of four")
-    ap.add_argument("--prefill", type=int, default=0, metavar="TOKENS",
-                    help="measure the tcgen05 prefill GEMM at this many tokens instead of the decode GEMV")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM section")
+    ap.add_argument("--no-decode", dest="decode", action="store_false", help="skip whole-model decoding")
+    ap.add_argument("--decode-batches", default="1,8", help="batch sizes of the whole-model decode section")
+    ap.set_defaults(decode=True)
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -276,20 +562,24 @@ def main() -> None:
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-
-    if args.prefill > 0:
-        run_prefill(args, device, rank, world)
+        try:
+            run_sharded(args, device, rank, world)
+        finally:
+            dist.barrier()
+            dist.destroy_process_group()
         return
+
     steps, warmup, m = max(args.steps, 1), max(args.warmup, 3), args.m
     copies = max(args.copies, 2)
-    layers = build_block(device, seed=rank, copies=copies, fuse=not args.no_fuse)
+    layers, per_layer = build_block(device, seed=rank, copies=copies, fuse=not args.no_fuse)
     step_bytes = sum(l["bytes"] for l in layers)
     flags = {"tiled": _lib.RDQ_GEMV_AUTO, "generic": _lib.RDQ_GEMV_GENERIC}[args.kernel]
     if not args.no_pdl:
         flags |= _lib.RDQ_GEMV_PDL
 
     gen = torch.Generator().manual_seed(1234 + rank)
-    xs = [torch.randn(m, l["k"], generator=gen).half().to(device) for l in layers]
+    xs_cpu = [torch.randn(m, l["k"], generator=gen).half() for l in layers]
+    xs = [x.to(device) for x in xs_cpu]
     ys = [torch.empty(m, l["n"], dtype=torch.float16, device=device) for l in layers]
 
     def one_step(i: int) -> None:
@@ -306,11 +596,12 @@ def main() -> None:
     torch.cuda.synchronize()
     # a kernel whose bounded waits ran out leaves a status word behind: stop here rather than
     # time steps that each sit through their wait limits
-    bad = sum(int(fd["tile_counters"].abs().sum().item()) for l in layers for fd in l["fds"] if "tile_counters" in fd)
-    if bad:
-        raise RuntimeError(f"GEMV kernels reported {bad} non-zero status words during warm-up")
+    for l in layers:
+        for fd in l["fds"]:
+            rdquant_cuda.check_status(fd)
     stream = torch.cuda.Stream(device)
     graph = torch.cuda.CUDAGraph()
+    replays = 10
     with torch.cuda.stream(stream):
         one_step(0)
         stream.synchronize()
@@ -321,22 +612,24 @@ def main() -> None:
         while time.time() - t_spin < 0.3:
             graph.replay()
             stream.synchronize()
-
-        if world > 1:
-            dist.barrier()
         torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0 = time.time()
-        e0.record(stream)
-        graph.replay()
-        e1.record(stream)
-        e1.synchronize()
+        times = time_replays(graph, stream, replays)
         torch.cuda.synchronize()
         t1 = time.time()
-        if world > 1:
-            dist.barrier()
-    ms = e0.elapsed_time(e1)
-    status_bad = sum(int(fd["tile_counters"].abs().sum().item()) for l in layers for fd in l["fds"])
+    ms = statistics.median(times)
+    clocks = sampler.stop(t0, t1)
+    for l in layers:
+        for fd in l["fds"]:
+            rdquant_cuda.check_status(fd)
+
+    # ---- parity of what was timed: the outputs of the last timed step against the CPU oracle
+    from oracle import oracle_np as onp
+
+    refs = [oracle_outputs(per_layer, l, xs_cpu[li].numpy()) for li, l in enumerate(layers)]
+    parity = max(float(onp.rel_err(ys[li].cpu().float().numpy(), refs[li])) for li in range(len(layers)))
+    if parity > TOL:
+        raise RuntimeError(f"timed outputs differ from the oracle: max rel err {parity:.3e} > {TOL}")
 
     # ---- end to end through the public API, host buffers in, host buffers out
     from rdquant_b200.inference import FusedMixedLinear, GraphedDecodeStep
@@ -352,73 +645,76 @@ def main() -> None:
     # one graphed step per weight copy, rotated like the device-only measurement
     runners = [GraphedDecodeStep(modules_of(c), m=m, use_pdl=not args.no_pdl) for c in range(copies)]
     for runner in runners:
-        for xh, x in zip(runner.x_host, xs):
-            xh.copy_(x.cpu())
+        for xh, x in zip(runner.x_host, xs_cpu):
+            xh.copy_(x)
     e2e_steps = min(steps, 200)
     for i in range(copies):
         runners[i].run()
-    if world > 1:
-        dist.barrier()
     te0 = time.perf_counter()
     for i in range(e2e_steps):
         # host activations in, host results out: one graph replay (H2D copies, GEMVs, D2H copies)
-        runners[i % copies].run()
+        y_host = runners[i % copies].run()
     te = time.perf_counter() - te0
-    clocks = sampler.stop(t0, t1)
+    e2e_parity = max(float(onp.rel_err(y_host[li].float().numpy(), refs[li])) for li in range(len(layers)))
+    if e2e_parity > TOL:
+        raise RuntimeError(f"end-to-end outputs differ from the oracle: max rel err {e2e_parity:.3e} > {TOL}")
+    del runners
 
-    # ---- max over ranks
-    if world > 1:
-        t = torch.tensor([ms, te], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, te = float(t[0]), float(t[1])
-
-    value = world * step_bytes * steps / (ms * 1e-3) / 1e9
-    e2e_value = world * step_bytes * e2e_steps / te / 1e9
+    value = step_bytes * steps / (ms * 1e-3) / 1e9
+    e2e_value = step_bytes * e2e_steps / te / 1e9
     peaks, peak_kind = measured_peaks()
     launches = steps * len(layers)
     per_launch_bytes = step_bytes / len(layers)
     achieved = per_launch_bytes / (ms * 1e-3 / launches) / 1e9
-    # dram__bytes_read + dram__bytes_write per launch from the ncu capture summarised in
-    # profiles/gemv_tiled_block_m1.md (average over the four fused launches of a step)
-    traffic = 19.46e6 if (m == 1 and not args.no_fuse and args.kernel == "tiled") else None
+    workload = f"block_m{m}" + ("" if not args.no_fuse else "_nofuse")
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16xf16->f32", "data": "synthetic",
         "config": {
-            "workload": f"qwen3-4b decoder block: q,k,v,o,gate,up,down mixed-precision linears, M={m} decode GEMV "
-                        "(BASELINE configs[1])",
+            "workload": f"qwen3-4b decoder block: q,k,v,o,gate,up,down mixed-precision linears, M={m} decode GEMV",
             "launches_per_step": len(layers),
             "fusion": "none" if args.no_fuse else "q/k/v and gate/up packed as one layer each (they read the same input)",
             "split": "67/32/1 NVFP4/FP8/FP16, 128-aligned, random channel permutation",
             "bytes_per_step": step_bytes, "l2_policy": f"{copies} rotating weight copies = "
             f"{copies * step_bytes / 1e6:.0f} MB > 2 x L2; inputs larger than L2, no flush",
-            "launch": "one CUDA graph of all timed steps, PDL-chained launches" if not args.no_pdl else "CUDA graph",
-            "parallelism": "1 block-sized column shard per GPU, no collective" if world > 1 else "single GPU",
+            "launch": ("one CUDA graph of all timed steps, PDL-chained launches" if not args.no_pdl else "CUDA graph")
+                      + "; median of %d replays" % replays,
+            "parallelism": "single GPU",
             "kernel": args.kernel,
         },
         "gpu_launches": launches,
+        "timing": {"replays": replays, "ms_per_step_median": ms / steps, "ms_per_step_min": min(times) / steps,
+                   "ms_per_step_max": max(times) / steps},
+        "parity_max_rel_err": max(parity, e2e_parity),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm_gbs"], "traffic": traffic, "peak_source": peak_kind,
+                     "frac": achieved / peaks["hbm_gbs"],
+                     "traffic": profiled_traffic("gemv_%s_kernel" % args.kernel, workload), "peak_source": peak_kind,
                      "frac_of_nominal_8tbs": achieved / 8000.0, "kernel": "gemv_%s_kernel" % args.kernel,
                      "bytes_per_launch": per_launch_bytes},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": sum(2 * m * l["k"] for l in layers),
                 "d2h_bytes_per_step": sum(2 * m * l["n"] for l in layers), "steps": e2e_steps,
                 "ms_per_step": 1e3 * te / e2e_steps,
-                "api": "inference.GraphedDecodeStep.run(): pinned host x -> device (staging kernel reading the pinned buffer), fused GEMVs, y -> pinned host (staging kernel) as one CUDA-graph replay, synchronised every step; weight copies rotate as in the device-only measurement"},
+                "api": "inference.GraphedDecodeStep.run(): pinned host x -> device (staging kernel reading the pinned "
+                       "buffer), fused GEMVs, y -> pinned host (staging kernel) as one CUDA-graph replay, synchronised "
+                       "every step; weight copies rotate as in the device-only measurement"},
         "clocks": clocks,
-        "status_words_nonzero": status_bad,
     }
-    if rank == 0:
-        if not args.no_cpu_baseline and world == 1:
-            base = cpu_baseline()
-            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        else:
-            line["cpu_baseline"] = None
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    if not args.no_prefill and m == 1:
+        line["prefill"] = prefill_section(device, layers)
+    for l in layers:
+        l["fds"] = l["fds"][:1]
+    torch.cuda.empty_cache()
+    if args.decode and m == 1:
+        batches = tuple(int(b) for b in args.decode_batches.split(",") if b)
+        line["decode"] = decode_section(device, batches=batches, gemv_block_ms=ms / steps)
+        line["config"]["decode_tokens_per_s"] = line["decode"]["batch"][str(batches[0])]["tokens_per_s"]
+    if not args.no_cpu_baseline:
+        base = cpu_baseline()
+        line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    else:
+        line["cpu_baseline"] = None
+    print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":

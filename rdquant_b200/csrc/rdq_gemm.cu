@@ -60,12 +60,9 @@ constexpr int kMaxBN = 256;
 // row); kTasks = groups a warp handles per k block.
 //   <1,128> <2,128>: 12 producer warps, 4 stages         (small problems)
 //   <2,256>        : 22 producer warps (768 threads), 3 x 64 KB stages, all 512 tensor-memory columns
-#ifndef RDQ_GEMM_PW
-#define RDQ_GEMM_PW 22
-#endif
 template <int MT, int BN>
 struct GemmCfg {
-  static constexpr int kProducerWarps = (BN == 128) ? 12 : RDQ_GEMM_PW;
+  static constexpr int kProducerWarps = (BN == 128) ? 12 : 22;
   static constexpr int kProducers = kProducerWarps * 32;
   static constexpr int kThreads = (2 + kProducerWarps) * 32;
   static constexpr int kStageB = BN * BK * 2;
@@ -75,10 +72,7 @@ struct GemmCfg {
   static constexpr int kSmem = kStages * (kStageAll + kStageB) + 1024;
   static constexpr int kMaxQuads = BN / 4 + 3;  // each format padded to a multiple of four rows
   static constexpr int kTasks = (kMaxQuads + kProducerWarps - 1) / kProducerWarps;
-#ifndef RDQ_GEMM_PF
-#define RDQ_GEMM_PF 1
-#endif
-  static constexpr int kPrefetch = RDQ_GEMM_PF;  // k blocks of packed weights held in registers ahead of use
+  static constexpr int kPrefetch = 1;  // k blocks of packed weights held in registers ahead of use
 };
 
 struct GemmSmem {

@@ -7,14 +7,6 @@ namespace {
 // time-out self-test).  Read and cleared by gemm_status().
 __device__ int g_gemm_status;
 
-#ifdef RDQ_GEMM_TIMELINE
-// debug build: per-k-block clocks of CTA (1, 1): [kb][0] MMA warp starts waiting, [1] stage full,
-// [2] MMAs issued; [3] producer thread 0 starts waiting for the empty stage, [4] got it, [5] arrived
-__device__ long long g_gtl[128 * 8];
-#define GTL(kb_, col_) do { if (blockIdx.x == 1 && blockIdx.y == 1 && (kb_) < 128) g_gtl[(kb_) * 8 + (col_)] = clock64(); } while (0)
-#else
-#define GTL(kb_, col_) do { } while (0)
-#endif
 
 __device__ __forceinline__ uint32_t ldg_nc2(const void *p) {
   uint16_t v;
@@ -124,9 +116,7 @@ __device__ __forceinline__ void produce_rows(GemmSmem &S, const GemmArgs &a, uin
     for (int p = 0; p < PF; ++p) {
       const int kb = kbase + p;
       if (kb >= nkb) break;
-      if (threadIdx.x == 64) GTL(kb, 3);
       cur.begin(S);
-      if (threadIdx.x == 64) GTL(kb, 4);
       const uint32_t sbase = b_base + cur.s * SB;
       // convert straight out of the prefetch registers, then refill them for k block kb + PF
 #pragma unroll
@@ -152,7 +142,6 @@ __device__ __forceinline__ void produce_rows(GemmSmem &S, const GemmArgs &a, uin
         if (kb + PF < nkb) q[p][t] = load(t, kb + PF);
       }
       cur.end(S);
-      if (threadIdx.x == 64) GTL(kb, 5);
     }
   }
 }
@@ -249,14 +238,10 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
         if (ph > 0) alive = gemm_wait(&S.empty[s], (ph - 1) & 1, &S.abort_flag);
         if (!alive) break;
         const uint32_t full = smem_u32(&S.full[s]);
-#ifdef RDQ_GEMM_SKIP_TMA  // debug experiment: no activation loads (results are wrong)
-        mbar_arrive(full);
-#else
         mbar_arrive_expect_tx(full, kStageAll);
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
           tma_load_2d(a_base + s * kStageAll + mt * kStageA, &xmap, kb * BK, m0 + mt * BM, full);
-#endif
         if (++s == NS) { s = 0; ++ph; }
       }
     }
@@ -267,10 +252,8 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
       bool alive = true;
       int s = 0, ph = 0;
       for (int kb = kb0; kb < nkb && alive; ++kb) {
-        GTL(kb, 0);
         alive = gemm_wait(&S.full[s], ph & 1, &S.abort_flag);
         if (!alive) break;
-        GTL(kb, 1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint64_t db = make_desc_sw128(b_base + s * SB);
 #pragma unroll
@@ -281,7 +264,6 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
             umma_f16(tmem + mt * BN, da + 2 * k4, db + 2 * k4, idesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
         }
         umma_commit(smem_u32(&S.empty[s]));
-        GTL(kb, 2);
         if (++s == NS) { s = 0; ++ph; }
       }
       umma_commit(smem_u32(&S.accum));
@@ -298,7 +280,6 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
     if (warp - 2 < kEpiWarps) {
       const bool ok = gemm_wait(&S.accum, 0, &S.abort_flag);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (threadIdx.x == 64) GTL(126, 0);
       const int q = warp & 3;  // tensor-memory lane quarter this warp may read
       const int sub = (warp - 2) >> 2;
       if (ok) {
@@ -376,7 +357,6 @@ gemm_mixed_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
     }
   }
 
-  if (threadIdx.x == 64) GTL(127, 0);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
@@ -472,11 +452,6 @@ GemmPlan gemm_plan(int M, int N, int K) {
 }
 }  // namespace
 
-#ifdef RDQ_GEMM_TIMELINE
-extern "C" int rdq_debug_gemm_timeline(long long *host_out) {
-  return cudaMemcpyFromSymbol(host_out, g_gtl, sizeof(long long) * 128 * 8) == cudaSuccess ? 0 : -3;
-}
-#endif
 
 namespace {
 std::atomic<int> g_gemm_test_timeout{0};

@@ -1,0 +1,217 @@
+"""A Qwen3-architecture decoder over the fused mixed-precision linears, for whole-model
+prefill / greedy-decode measurements on synthetic weights (BASELINE configs 4 and 5; the
+reference's harness is benchmarks/bench_e2e.py:103-155 over a HuggingFace model).
+
+Everything that is not a linear layer -- embedding lookup, RMSNorm, rotary embedding, the
+attention over the KV cache, SiLU x mul, the residual adds, the FP16 lm_head and the arg-max --
+is plain PyTorch: it is glue around the operator this package provides, not part of it.  q/k/v
+and gate/up are packed as one layer each (they read the same input).  A decode step has static
+shapes (the KV cache is allocated for the whole run, the current position lives in a device
+tensor), so it is captured once in a CUDA graph and replayed per token.
+
+With ``world > 1`` every linear is column-parallel (``parallel.ColumnParallelMixedLinear``):
+each rank streams its rows and one NCCL all-gather per linear rebuilds the full activation on
+every rank; the glue is computed redundantly on all ranks.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from rdquant_b200.fused_gemv_pack import fuse_layers, packed_weight_bytes
+from rdquant_b200.quantize import quantize_weight_packed
+
+
+@dataclass
+class DecoderConfig:
+    layers: int = 36
+    hidden: int = 2560
+    ffn: int = 9728
+    q_heads: int = 32
+    kv_heads: int = 8
+    head_dim: int = 128
+    vocab: int = 151936
+    qk_norm: bool = True
+    rope_theta: float = 1.0e6
+    eps: float = 1.0e-6
+    frac_fp4: float = 0.67
+    frac_fp16: float = 0.01
+    name: str = "qwen3-4b-shaped"
+
+
+QWEN3_4B = DecoderConfig()
+LLAMA3_70B = DecoderConfig(layers=80, hidden=8192, ffn=28672, q_heads=64, kv_heads=8, head_dim=128, vocab=128256,
+                           qk_norm=False, rope_theta=5.0e5, eps=1.0e-5, frac_fp4=0.85, frac_fp16=0.0,
+                           name="llama3-70b-shaped")
+
+
+def _splits(n_out: int, cfg: DecoderConfig) -> dict:
+    """Channel counts per format: the configured fractions rounded to 128 channels (layers
+    narrower than three tiles: to 16 channels, like synthetic.fixed_splits)."""
+    unit = 128 if n_out >= 384 else 16
+    rnd = lambda v: int(round(v / unit)) * unit  # noqa: E731
+    n16 = max(unit, rnd(cfg.frac_fp16 * n_out)) if cfg.frac_fp16 > 0 else 0
+    n4 = min(rnd(cfg.frac_fp4 * n_out), n_out - n16)
+    return {"NVFP4": n4, "FP8": n_out - n4 - n16, "FP16": n16}
+
+
+def _rms(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
+def _rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x [B, T, H, D]; cos / sin [T, D] (halves duplicated, HuggingFace convention)."""
+    d = x.shape[-1] // 2
+    rot = torch.cat([-x[..., d:], x[..., :d]], dim=-1)
+    return x * cos[None, :, None, :] + rot * sin[None, :, None, :]
+
+
+class MixedDecoder:
+    """Random-init decoder; weights are generated, encoded and packed layer by layer on the GPU."""
+
+    def __init__(self, cfg: DecoderConfig, device, max_seq: int, batch: int, seed: int = 0, rank: int = 0,
+                 world: int = 1, group=None, use_pdl: bool = True) -> None:
+        self.cfg, self.device, self.max_seq, self.batch = cfg, torch.device(device), max_seq, batch
+        self.rank, self.world, self.group = rank, world, group
+        gen = torch.Generator(device=self.device).manual_seed(seed)
+        h, dh = cfg.hidden, cfg.head_dim
+        nq, nkv = cfg.q_heads * dh, cfg.kv_heads * dh
+        self.linear_bytes = 0       # packed weight + scale bytes of all linears (whole model)
+        self.local_linear_bytes = 0  # ... of this rank's rows
+        self.blocks = []
+        for _ in range(cfg.layers):
+            blk = {
+                "qkv": self._linear([(h, nq), (h, nkv), (h, nkv)], gen, use_pdl),
+                "o": self._linear([(nq, h)], gen, use_pdl),
+                "gate_up": self._linear([(h, cfg.ffn), (h, cfg.ffn)], gen, use_pdl),
+                "down": self._linear([(cfg.ffn, h)], gen, use_pdl),
+                "ln1": torch.ones(h, dtype=torch.float16, device=self.device),
+                "ln2": torch.ones(h, dtype=torch.float16, device=self.device),
+                "qn": torch.ones(dh, dtype=torch.float16, device=self.device),
+                "kn": torch.ones(dh, dtype=torch.float16, device=self.device),
+            }
+            self.blocks.append(blk)
+        self.embed = (torch.randn(cfg.vocab, h, generator=gen, device=self.device, dtype=torch.float32) * 0.02).half()
+        self.lm_head = self.embed  # tied, FP16 (not quantised), like the checkpoint's embed / lm_head
+        self.norm = torch.ones(h, dtype=torch.float16, device=self.device)
+        inv_freq = 1.0 / (cfg.rope_theta ** (torch.arange(0, dh, 2, device=self.device).float() / dh))
+        ang = torch.arange(max_seq, device=self.device).float()[:, None] * inv_freq[None, :]
+        self.cos = torch.cat([ang.cos(), ang.cos()], dim=-1).half()
+        self.sin = torch.cat([ang.sin(), ang.sin()], dim=-1).half()
+        self.positions = torch.arange(max_seq, device=self.device)
+        self.reset(batch)
+
+    def reset(self, batch: int) -> None:
+        """(Re)allocate the KV cache and the step state for `batch` sequences; drops a captured graph."""
+        cfg = self.cfg
+        self.batch = batch
+        self._graph = None
+        for blk in self.blocks:
+            blk["k"] = torch.zeros(batch, cfg.kv_heads, self.max_seq, cfg.head_dim, dtype=torch.float16, device=self.device)
+            blk["v"] = torch.zeros(batch, cfg.kv_heads, self.max_seq, cfg.head_dim, dtype=torch.float16, device=self.device)
+        self.pos = torch.zeros(1, dtype=torch.long, device=self.device)      # next position to write
+        self.ids = torch.zeros(batch, dtype=torch.long, device=self.device)  # tokens fed to the next step
+
+    # ---- construction
+    def _linear(self, shapes, gen, use_pdl):
+        cfg = self.cfg
+        parts = []
+        for k, n in shapes:
+            w = (torch.randn(n, k, generator=gen, device=self.device, dtype=torch.float32) * 0.02)
+            idx = torch.randperm(n, generator=gen, device=self.device)[: n // 100]
+            w[idx] *= 8
+            perm = torch.randperm(n, generator=gen, device=self.device)
+            sp = _splits(n, cfg)
+            parts.append((quantize_weight_packed(w.half(), perm, sp), sp))
+            self.linear_bytes += packed_weight_bytes(sp, k)
+            del w
+        k = shapes[0][0]
+        data, sp = fuse_layers(parts) if len(parts) > 1 else parts[0]
+        if self.world > 1:
+            from rdquant_b200.parallel import ColumnParallelMixedLinear
+
+            mod = ColumnParallelMixedLinear(data, sp, k, self.device, self.rank, self.world, self.group)
+            self.local_linear_bytes += mod.packed_bytes()
+        else:
+            from rdquant_b200.inference import FusedMixedLinear
+
+            mod = FusedMixedLinear.from_layer_data(data, sp, k, self.device)
+            self.local_linear_bytes += packed_weight_bytes(sp, k)
+        mod.use_pdl = use_pdl
+        return mod
+
+    # ---- one forward pass over `t` new tokens per sequence, written at positions pos .. pos + t - 1
+    def _forward(self, ids: torch.Tensor, t: int, pos0) -> torch.Tensor:
+        """ids [B, t]; pos0: int (prefill) or the device tensor self.pos (graphed decode, t == 1).
+        Returns the logits of the last position [B, vocab]."""
+        cfg = self.cfg
+        b = ids.shape[0]
+        x = self.embed[ids]  # [B, t, H]
+        if isinstance(pos0, int):
+            cos, sin = self.cos[pos0:pos0 + t], self.sin[pos0:pos0 + t]
+            idx = self.positions[pos0:pos0 + t]
+            mask = (self.positions[None, :] <= idx[:, None])[None, None]  # [1, 1, t, S]
+        else:
+            cos, sin = self.cos.index_select(0, pos0), self.sin.index_select(0, pos0)
+            idx = pos0
+            mask = (self.positions <= pos0)[None, None, None, :]  # [1, 1, 1, S]
+        nq, nkv, dh = cfg.q_heads, cfg.kv_heads, cfg.head_dim
+        for blk in self.blocks:
+            hcur = _rms(x, blk["ln1"], cfg.eps)
+            qkv = blk["qkv"](hcur)
+            q = qkv[..., : nq * dh].reshape(b, t, nq, dh)
+            k = qkv[..., nq * dh:(nq + nkv) * dh].reshape(b, t, nkv, dh)
+            v = qkv[..., (nq + nkv) * dh:].reshape(b, t, nkv, dh)
+            if cfg.qk_norm:
+                q, k = _rms(q, blk["qn"], cfg.eps), _rms(k, blk["kn"], cfg.eps)
+            q, k = _rope(q, cos, sin), _rope(k, cos, sin)
+            blk["k"].index_copy_(2, idx, k.transpose(1, 2))
+            blk["v"].index_copy_(2, idx, v.transpose(1, 2))
+            att = F.scaled_dot_product_attention(q.transpose(1, 2), blk["k"], blk["v"], attn_mask=mask, enable_gqa=True)
+            x = x + blk["o"](att.transpose(1, 2).reshape(b, t, nq * dh))
+            hcur = _rms(x, blk["ln2"], cfg.eps)
+            gu = blk["gate_up"](hcur)
+            x = x + blk["down"](F.silu(gu[..., : cfg.ffn]) * gu[..., cfg.ffn:])
+        last = _rms(x[:, -1], self.norm, cfg.eps)
+        return last @ self.lm_head.T
+
+    @torch.no_grad()
+    def prefill(self, ids: torch.Tensor) -> torch.Tensor:
+        """Run the prompt [B, T] (GEMM path), fill the KV cache, return the first generated ids."""
+        t = ids.shape[1]
+        logits = self._forward(ids, t, 0)
+        self.pos.fill_(t)
+        self.ids.copy_(logits.argmax(-1))
+        return self.ids.clone()
+
+    def _step(self) -> None:
+        logits = self._forward(self.ids[:, None], 1, self.pos)
+        self.ids.copy_(logits.argmax(-1))
+        self.pos.add_(1)
+
+    @torch.no_grad()
+    def capture_decode(self) -> None:
+        """Capture one decode step (static shapes) into a CUDA graph; replay with ``decode_step``."""
+        pos_saved, ids_saved = self.pos.clone(), self.ids.clone()
+        stream = torch.cuda.Stream(self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            for _ in range(2):  # warm-up outside capture: lazy initialisation, buffer allocation
+                self._step()
+            stream.synchronize()
+            self._graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self._graph, stream=stream):
+                self._step()
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        self.pos.copy_(pos_saved)
+        self.ids.copy_(ids_saved)
+
+    @torch.no_grad()
+    def decode_step(self) -> None:
+        if self._graph is None:
+            self._step()
+        else:
+            self._graph.replay()

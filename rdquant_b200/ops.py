@@ -15,7 +15,7 @@ import torch
 from rdquant_b200.core.formats import QuantizedTensor
 
 _PACK_CACHE: "OrderedDict[int, tuple]" = OrderedDict()
-_PACK_CACHE_MAX = 1024
+_PACK_CACHE_MAX = 128  # packed layers kept alive for reuse (each entry also pins its qtensors dict)
 
 
 def _packed_for(qtensors: dict, splits: dict, inv_perm: torch.Tensor, device: torch.device) -> dict:

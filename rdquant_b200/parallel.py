@@ -6,8 +6,13 @@ order) is cut at 128-channel boundaries into ``world`` contiguous row ranges -- 
 slice of the packed checkpoint tensors, the on-disk layout is unchanged.  Every rank runs
 the fused kernels on its rows (x replicated, no collective on that path).  Where the full
 output vector is needed on every rank (whole-model decode) one NCCL ``all_gather`` per layer
-collects the ``[M, N_r]`` slices; the kernel writes its slice in local permuted order and a
+collects the ``[M, n_max]`` slices; the kernel writes its slice in local permuted order and a
 precomposed index restores original channel order after the gather.
+
+Ranks whose share is narrower than the widest one get zero-weight rows appended at pack time
+(NVFP4 codes 0 with block scale 0: 0.56 bytes per element), so every rank's kernel writes a
+full ``[M, n_max]`` slice straight into the send buffer: no pad copy, no allocation, and the
+whole forward -- kernel, all-gather, one ``take`` -- can sit inside a CUDA graph.
 """
 from __future__ import annotations
 
@@ -42,7 +47,8 @@ class ColumnParallelPlan:
     splits: dict            # full layer
     ranges: dict            # fmt -> list of world + 1 offsets inside the group
     n_local: list           # rows owned by each rank
-    n_max: int              # widest rank (gather buffers are padded to this)
+    n_max: int              # widest rank (every rank's slice is padded to this)
+    pad_format: str         # format group that receives a rank's zero rows
     gather_index: torch.Tensor  # int64 [N]: position of original channel j in the [world, n_max] gather buffer
 
     @classmethod
@@ -52,7 +58,9 @@ class ColumnParallelPlan:
         n_local = [sum(ranges[f][r + 1] - ranges[f][r] for f in FORMAT_ORDER) for r in range(world)]
         n_max = max(n_local) if n_local else 0
         n = sum(sizes.values())
-        # position of every permuted row p in the gathered [world, n_max] buffer
+        pad_format = next((f for f in FORMAT_ORDER if sizes[f] > 0), "NVFP4")
+        # position of every permuted row p in the gathered [world, n_max] buffer; a rank's zero
+        # rows sit at the end of its pad_format group
         pos_of_perm_row = torch.empty(n, dtype=torch.int64)
         for r in range(world):
             local = 0
@@ -62,34 +70,65 @@ class ColumnParallelPlan:
                 if hi > lo:
                     pos_of_perm_row[start + lo:start + hi] = r * n_max + local + torch.arange(hi - lo)
                 local += hi - lo
+                if f == pad_format:
+                    local += n_max - n_local[r]
         inv = inv_perm.to(torch.int64).cpu()
-        return cls(world, sizes, ranges, n_local, n_max, pos_of_perm_row[inv])
+        return cls(world, sizes, ranges, n_local, n_max, pad_format, pos_of_perm_row[inv])
 
-    def local_splits(self, rank: int) -> dict:
-        return {f: self.ranges[f][rank + 1] - self.ranges[f][rank] for f in FORMAT_ORDER}
-
-    def shard_layer_data(self, layer_data: dict, rank: int) -> dict:
-        """Row slices of the packed tensors owned by ``rank`` (identity local permutation)."""
-        out = {}
-        for f in FORMAT_ORDER:
-            lo, hi = self.ranges[f][rank], self.ranges[f][rank + 1]
-            if hi == lo:
-                continue
-            for key in _KEYS[f]:
-                out[key] = layer_data[key][lo:hi].contiguous()
-            if f == "NVFP4" and "nvfp4_global_scale" in layer_data:
-                out["nvfp4_global_scale"] = layer_data["nvfp4_global_scale"]
-        out["inv_permutation"] = torch.arange(self.n_local[rank], dtype=torch.int32)
+    def local_splits(self, rank: int, padded: bool = True) -> dict:
+        out = {f: self.ranges[f][rank + 1] - self.ranges[f][rank] for f in FORMAT_ORDER}
+        if padded:
+            out[self.pad_format] += self.n_max - self.n_local[rank]
         return out
 
+    def shard_layer_data(self, layer_data: dict, rank: int, padded: bool = True) -> dict:
+        """Row slices of the packed tensors owned by ``rank`` (identity local permutation), with
+        the rank's zero rows appended to the ``pad_format`` group when ``padded``."""
+        out = {}
+        pad = self.n_max - self.n_local[rank] if padded else 0
+        for f in FORMAT_ORDER:
+            lo, hi = self.ranges[f][rank], self.ranges[f][rank + 1]
+            extra = pad if f == self.pad_format else 0
+            if hi == lo and extra == 0:
+                continue
+            for key in _KEYS[f]:
+                part = layer_data[key][lo:hi]
+                if extra:
+                    fill = 1.0 if key == "weight_fp8_scale" else 0
+                    zeros = torch.full((extra,) + tuple(part.shape[1:]), fill, dtype=part.dtype, device=part.device)
+                    part = torch.cat([part, zeros], dim=0)
+                out[key] = part.contiguous()
+            if f == "NVFP4" and "nvfp4_global_scale" in layer_data:
+                out["nvfp4_global_scale"] = layer_data["nvfp4_global_scale"]
+        out["inv_permutation"] = torch.arange(self.n_local[rank] + pad, dtype=torch.int32)
+        return out
+
+    def local_bias(self, bias: torch.Tensor, rank: int) -> torch.Tensor:
+        """``bias`` (original channel order) rearranged to ``rank``'s padded slice order."""
+        flat = torch.zeros(self.world * self.n_max, dtype=bias.dtype)
+        flat[self.gather_index] = bias.detach().cpu()
+        return flat[rank * self.n_max:(rank + 1) * self.n_max].contiguous()
+
+    def take_index(self, m: int) -> torch.Tensor:
+        """int64 ``[m, N]``: flat positions inside a ``[world, m, n_max]`` gather buffer of
+        ``y[row, original channel]``."""
+        r = self.gather_index // self.n_max
+        c = self.gather_index - r * self.n_max
+        rows = torch.arange(m, dtype=torch.int64).unsqueeze(1)
+        return (r.unsqueeze(0) * m + rows) * self.n_max + c.unsqueeze(0)
+
     def packed_bytes(self, rank: int, k: int) -> int:
-        s = self.local_splits(rank)
+        s = self.local_splits(rank, padded=False)
         return s["NVFP4"] * (k // 2 + k // 16) + s["FP8"] * (k + 4) + s["FP16"] * 2 * k
 
 
 def gather_outputs(y_local: torch.Tensor, plan: ColumnParallelPlan, group=None,
-                   buffer: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """All-gather the ``[M, n_local]`` slices and return ``[M, N]`` in original channel order."""
+                   buffer: Optional[torch.Tensor] = None, index: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """All-gather the per-rank slices and return ``[M, N]`` in original channel order.
+
+    ``y_local`` is ``[M, n_max]`` (padded slice) or ``[M, n_local]`` (then it is padded here,
+    which costs a copy); ``buffer`` ``[world, M, n_max]`` and ``index`` (``plan.take_index(M)`` on
+    the device) may be passed in to make the call allocation-free."""
     import torch.distributed as dist
 
     m = y_local.shape[0]
@@ -101,34 +140,64 @@ def gather_outputs(y_local: torch.Tensor, plan: ColumnParallelPlan, group=None,
     if buffer is None:
         buffer = y_local.new_empty(world, m, plan.n_max)
     dist.all_gather_into_tensor(buffer.view(world * m, plan.n_max), send.contiguous(), group=group)
-    flat = buffer.permute(1, 0, 2).reshape(m, world * plan.n_max)
-    return flat.index_select(1, plan.gather_index.to(flat.device))
+    if index is None:
+        index = plan.take_index(m).to(buffer.device)
+    return torch.take(buffer, index)
 
 
 class ColumnParallelMixedLinear(nn.Module):
-    """One rank's share of a mixed-precision linear plus the all-gather of the outputs."""
+    """One rank's share of a mixed-precision linear plus the all-gather of the outputs.
+
+    Buffers (send slice, gather buffer, un-permute index) are allocated once per activation row
+    count, so a forward pass is: one fused kernel launch, one ``all_gather_into_tensor``, one
+    ``take`` -- all capturable in a CUDA graph.  The bias is added by the kernel's epilogue."""
 
     def __init__(self, layer_data: dict, splits: dict, k: int, device, rank: int, world: int, group=None,
                  gather: bool = True) -> None:
         super().__init__()
-        from rdquant_b200.inference import FusedMixedLinear
+        from rdquant_b200.fused_gemv_pack import pack_for_fused_gemv
 
         self.plan = ColumnParallelPlan.build(splits, layer_data["inv_permutation"], world)
         self.rank, self.world, self.group, self.gather = rank, world, group, gather
         self.K = int(k)
         self.N = sum(self.plan.splits.values())
+        self.device = torch.device(device)
         shard = self.plan.shard_layer_data(layer_data, rank)
-        self.local = FusedMixedLinear.from_layer_data(shard, self.plan.local_splits(rank), k, device)
+        self.local_splits = self.plan.local_splits(rank)
+        self.fd = pack_for_fused_gemv(shard, self.local_splits, k, device)
+        if self.fd is None:
+            raise RuntimeError("rdquant_b200 kernels unavailable: build librdq_b200.so and run on a CUDA device")
         bias = layer_data.get("bias")
-        self.bias = nn.Parameter(bias.to(device)) if bias is not None else None
-        self.register_buffer("_gather_index", self.plan.gather_index.to(device), persistent=False)
+        self.bias_local = None
+        if bias is not None:
+            self.bias_local = self.plan.local_bias(bias, rank).to(device=self.device, dtype=torch.float16)
+        self.use_pdl = False
+        self._state: dict = {}
+
+    def _buffers(self, m: int):
+        st = self._state.get(m)
+        if st is None:
+            send = torch.zeros(m, self.plan.n_max, dtype=torch.float16, device=self.device)
+            buf = torch.zeros(self.world, m, self.plan.n_max, dtype=torch.float16, device=self.device)
+            idx = self.plan.take_index(m).to(self.device)
+            st = (send, buf, idx)
+            self._state[m] = st
+        return st
+
+    def packed_bytes(self) -> int:
+        return self.plan.packed_bytes(self.rank, self.K)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        from rdquant_b200 import _lib, rdquant_cuda
+
         lead = x.shape[:-1]
-        y_local = self.local(x.reshape(-1, self.K))
+        x2 = x.reshape(-1, self.K)
+        xh = (x2 if x2.dtype == torch.float16 else x2.half()).contiguous()
+        m = xh.shape[0]
+        send, buf, idx = self._buffers(m)
+        flags = _lib.RDQ_GEMV_PDL if self.use_pdl else 0
+        rdquant_cuda.mixed_linear(xh, self.fd, self.bias_local, flags, out=send)
         if not self.gather:
-            return y_local
-        y = gather_outputs(y_local, self.plan, self.group)
-        if self.bias is not None:
-            y = y + self.bias.to(y.dtype)
-        return y.reshape(*lead, self.N)
+            return send
+        y = gather_outputs(send, self.plan, self.group, buffer=buf, index=idx)
+        return y.to(x.dtype).reshape(*lead, self.N)

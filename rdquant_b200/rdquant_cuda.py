@@ -100,6 +100,22 @@ def check_gemm_status(device) -> None:
     _lib.check(rc, "rdq_gemm_status")
 
 
+_scratch_by_device: dict = {}
+
+
+def _shared_scratch(device) -> tuple[torch.Tensor, torch.Tensor]:
+    """One scratch pair per device for callers that bring none (the reference-signature entry
+    point): the kernel leaves it idle after every launch, and launches on one device are ordered
+    by the current stream."""
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    pair = _scratch_by_device.get(key)
+    if pair is None:
+        pair = gemv_scratch(0, device)
+        _scratch_by_device[key] = pair
+    return pair
+
+
 def dequantize_packed(layer_data: dict, splits: dict, k: int, inv_perm: Optional[torch.Tensor] = None,
                       out_dtype: torch.dtype = torch.float16, global_scale: float = 1.0) -> torch.Tensor:
     """Dequantise packed checkpoint tensors to ``[N, K]`` in original channel order.
@@ -209,7 +225,8 @@ def mixed_gemv(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None, f
 _gemm_ws: dict = {}  # device -> scratch tensor of the split-k GEMM
 
 
-def mixed_gemm(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+def mixed_gemm(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Prefill GEMM ``y[M, N] = x[M, K] @ W.T (+ bias)`` on the tcgen05 path."""
     _need_cuda("x", x, torch.float16)
     if x.dim() != 2:
@@ -221,7 +238,9 @@ def mixed_gemm(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None) -
     n = n4 + n8 + n16
     if bias is not None:
         _need_cuda("bias", bias, torch.float16)
-    y = torch.empty(m, n, dtype=torch.float16, device=x.device)
+    y = out if out is not None else torch.empty(m, n, dtype=torch.float16, device=x.device)
+    if out is not None and (tuple(out.shape) != (m, n) or out.dtype != torch.float16 or not out.is_contiguous()):
+        raise RuntimeError("out must be a contiguous float16 [M, N] tensor")
     if m == 0 or n == 0:
         return y
     with _on_device(x.device):
@@ -245,16 +264,17 @@ def mixed_gemm(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None) -
     return y
 
 
-def mixed_linear(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None, flags: int = 0) -> torch.Tensor:
+def mixed_linear(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None, flags: int = 0,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """GEMV for M <= 16, GEMM above."""
     if x.shape[0] <= MAX_GEMV_M:
-        return mixed_gemv(x, fd, bias, flags)
+        return mixed_gemv(x, fd, bias, flags, out=out)
     if fd["k"] % 64 == 0:
-        return mixed_gemm(x, fd, bias)
+        return mixed_gemm(x, fd, bias, out=out)
     # the tensor-core GEMM tiles K in blocks of 64; other K run the decode kernel over 16-row
     # panels (the reference's dense prefill takes any K, rdquant/inference.py:679-687)
     n = fd["n_fp4"] + fd["n_fp8"] + fd["n_fp16"]
-    y = torch.empty(x.shape[0], n, dtype=torch.float16, device=x.device)
+    y = out if out is not None else torch.empty(x.shape[0], n, dtype=torch.float16, device=x.device)
     for r0 in range(0, x.shape[0], MAX_GEMV_M):
         mixed_gemv(x[r0:r0 + MAX_GEMV_M], fd, bias, flags, out=y[r0:r0 + MAX_GEMV_M])
     return y
@@ -283,7 +303,7 @@ def fused_mixed_gemv(x: torch.Tensor, w_fp4: torch.Tensor, w_fp4_scales: torch.T
         raise RuntimeError("w_fp8 must be [N_fp8, K] and w_fp8_scales [N_fp8]")
     if inv_perm.numel() != N_fp4 + N_fp8:
         raise RuntimeError("inv_perm must have N_fp4 + N_fp8 elements")
-    ws, cnt = gemv_scratch(N_fp4 + N_fp8, x.device)
+    ws, cnt = _shared_scratch(x.device)
     fd = {
         "w_fp4_q": w_fp4 if N_fp4 else None, "w_fp4_scales": w_fp4_scales if N_fp4 else None,
         "w_fp4_global_scale": float(w_fp4_global_scale),

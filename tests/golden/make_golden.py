@@ -14,7 +14,10 @@ Writes
                     checkpoint bytes (float16; the FP16 group passes through bfloat16
                     there), and the reference operator's output
   config1_alloc.npz permutation / splits chosen by the reference's Lagrangian allocator for
-                    the K=2560, N=9728 layer at 5.3 average bits (seed 0)
+                    the K=2560, N=9728 layer at 5.3 average bits (seed 0), SHA-256 of the source
+                    weight, of every tensor the reference's save_packed wrote for it and of its
+                    dequantised weight, 24 rows of that weight, and the reference operator's
+                    output for a seeded activation row
 """
 import os
 import sys
@@ -122,7 +125,18 @@ def layers():
     print({k: v.tolist() for k, v in out.items() if k.endswith("/splits")})
 
 
+def _sha(t: torch.Tensor) -> np.ndarray:
+    import hashlib
+
+    raw = t.contiguous().view(torch.uint8).numpy().tobytes()
+    return np.frombuffer(hashlib.sha256(raw).digest(), dtype=np.uint8).copy()
+
+
 def config1():
+    """BASELINE configs[0] at full size: K = 2560, N = 9728, seed 0, allocator at 5.3 bits.  The
+    weight itself is regenerated from the seed by the tests; pinned here are its hash, the
+    allocator's result, hashes of the reference's packed checkpoint tensors and of its
+    dequantised weight, a few rows of that weight, and the reference operator's output."""
     g = torch.Generator().manual_seed(0)
     n, k = 9728, 2560
     w = (torch.randn(n, k, generator=g) * 0.02).half()
@@ -130,9 +144,29 @@ def config1():
     w[idx] *= 8
     alloc = allocate_layer(w.float(), 5.3, ORDER)
     print("config1 splits", alloc.splits, "avg bits", alloc.avg_bits)
+    qw = _quantize_weight(w.float(), alloc)
+    x = torch.randn(1, k, generator=g).half()
+    y = mixed_precision_linear(x, qw.qtensors, qw.splits, qw.inv_permutation, None)
+    w_ref = qw.dequantize().half()  # [N, K] original order
+    layer = QuantizedLayer(qw, None, k, n)
+    holder = torch.nn.Module()
+    holder.add_module("fc", layer)
+    qm = QuantizedModel(model=holder, layer_info={}, formats=ORDER, budget_avg_bits=5.3)
+    from safetensors import safe_open
+    hashes = {}
+    with tempfile.TemporaryDirectory() as d:
+        save_packed(qm, d)
+        with safe_open(os.path.join(d, "model.safetensors"), framework="pt", device="cpu") as fh:
+            for key in fh.keys():
+                t = fh.get_tensor(key)
+                hashes["sha_" + key[len("fc."):]] = _sha(t)
+    rows = np.linspace(0, n - 1, 24).astype(np.int64)
     np.savez_compressed(os.path.join(HERE, "config1_alloc.npz"), perm=alloc.permutation.numpy().astype(np.int32),
                         splits=np.array([alloc.splits.get(f, 0) for f in ORDER], dtype=np.int32),
-                        avg_bits=np.float64(alloc.avg_bits))
+                        avg_bits=np.float64(alloc.avg_bits), sha_weight_f16=_sha(w), sha_w_ref_f16=_sha(w_ref),
+                        sample_rows=rows, w_ref_rows_f16_bits=w_ref[rows].view(torch.int16).numpy().view(np.uint16),
+                        x_f16_bits=x.view(torch.int16).numpy().view(np.uint16),
+                        y_ref_f16_bits=y.view(torch.int16).numpy().view(np.uint16), **hashes)
 
 
 if __name__ == "__main__":

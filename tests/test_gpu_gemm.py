@@ -86,3 +86,43 @@ def test_large_tiles(m, n, k):
     splits = dict(zip(ORDER, (n4, n8, n16)))
     y, y_ref = _run(layer, splits, k, m, bias=True, seed=5)
     assert onp.rel_err(y, y_ref) < TOL
+
+
+@pytest.mark.parametrize("m", [512, 2048, 8192])
+@pytest.mark.parametrize("group", [["q_proj", "k_proj", "v_proj"], ["o_proj"], ["gate_proj", "up_proj"], ["down_proj"]])
+def test_benchmark_launches(group, m):
+    """The four launches the prefill benchmark times -- q+k+v (2560 -> 6144) and gate+up
+    (2560 -> 19456) packed as one layer each by fuse_layers, o and down as they are -- at its three
+    token counts.  Every member layer is compared with the oracle on a seeded sample of 64 rows
+    (the CPU side stays in seconds at M = 8192), and the whole output with x @ dequant(W)^T, the
+    weight coming from the bit-exact dequantisation kernel."""
+    from rdquant_b200.fused_gemv_pack import fuse_layers
+
+    members = []
+    for i, name in enumerate(group):
+        k, n = QWEN3_4B_BLOCK[name]
+        splits = fixed_splits(n)
+        members.append((random_packed_layer(splits["NVFP4"], splits["FP8"], splits["FP16"], k, seed=51 + i), splits))
+    k = QWEN3_4B_BLOCK[group[0]][0]
+    data, splits = fuse_layers(members) if len(members) > 1 else members[0]
+    fd = pack_for_fused_gemv(data, splits, k, "cuda", tiled=False)
+    gen = torch.Generator().manual_seed(m)
+    x = torch.randn(m, k, generator=gen).half().cuda()
+    y = rdquant_cuda.mixed_gemm(x, fd)
+    rdquant_cuda.check_gemm_status(x.device)
+    rows = torch.randperm(m, generator=gen)[:64].sort().values
+    xs, ys = x[rows.cuda()].cpu().numpy(), y[rows.cuda()].cpu().float().numpy()
+    off = 0
+    for layer, sp in members:
+        n = sum(sp.values())
+        y_ref = onp.mixed_precision_linear(xs, onp.torch_layer_to_np(layer), sp, k)
+        assert onp.rel_err(ys[:, off:off + n], y_ref) < TOL, (group, m, off)
+        off += n
+    assert off == y.shape[1]
+    dev = {kk: v.cuda() for kk, v in data.items()}
+    w = rdquant_cuda.dequantize_packed(dev, splits, k, inv_perm=dev["inv_permutation"])
+    worst = 0.0
+    for r0 in range(0, m, 2048):  # in panels: the FP32 product of the full problem would take gigabytes
+        ref = x[r0:r0 + 2048].float() @ w.float().T
+        worst = max(worst, float((y[r0:r0 + 2048].float() - ref).abs().max() / ref.abs().max()))
+    assert worst < TOL

@@ -36,7 +36,20 @@ def test_plan_covers_every_channel_once():
         assert plan.gather_index.unique().numel() == 1024
         assert int(plan.gather_index.max()) < world * plan.n_max
         for r in range(world):
-            assert sum(plan.local_splits(r).values()) == plan.n_local[r]
+            assert sum(plan.local_splits(r, padded=False).values()) == plan.n_local[r]
+            assert sum(plan.local_splits(r).values()) == plan.n_max  # zero rows fill the narrower ranks
+            shard = plan.shard_layer_data({"weight_nvfp4": torch.zeros(640, 8, dtype=torch.uint8),
+                                           "weight_nvfp4_scale": torch.zeros(640, 1, dtype=torch.uint8),
+                                           "weight_fp8": torch.zeros(256, 16, dtype=torch.uint8),
+                                           "weight_fp8_scale": torch.ones(256),
+                                           "weight_fp16": torch.zeros(128, 16, dtype=torch.bfloat16)}, r)
+            assert shard["inv_permutation"].numel() == plan.n_max
+            assert shard["weight_nvfp4"].shape[0] == plan.local_splits(r)["NVFP4"]
+        idx = plan.take_index(3)
+        assert idx.shape == (3, 1024) and int(idx.max()) < world * 3 * plan.n_max and idx.unique().numel() == 3 * 1024
+        bias = torch.arange(1024, dtype=torch.float32)
+        locals_ = torch.cat([plan.local_bias(bias, r) for r in range(world)])
+        assert torch.equal(locals_[plan.gather_index], bias)
 
 
 def _worker(rank, world, port, case_name, out_q):
