@@ -278,6 +278,45 @@ int rdq_quantize_fp8(const void *w, int w_is_f32, int n, int K,
                      float *absmax_scratch, void *stream);
 
 /*
+ * Decode-step glue: the small operations between the linears of a transformer
+ * block at one token per sequence, as kernels that take part in programmatic
+ * dependent launch like the GEMV (flags: RDQ_GEMV_PDL) -- each lets the next
+ * kernel start at once, so the following GEMV fills its weight rings meanwhile,
+ * and reads its inputs only after the preceding kernel has finished.  The
+ * reference leaves this code to the HuggingFace model around its modules
+ * (module boundary rdquant/inference.py:689-708; harness
+ * benchmarks/bench_e2e.py:103-155).  All tensors f16 unless stated, row-major.
+ *   rdq_add_rmsnorm     x[B,H] += delta[B,H] (delta may be NULL: no add);
+ *                       out[B,H] = f16(x * rsqrt(mean(x^2) + eps)) * weight[H]
+ *   rdq_qk_rope_cache   qkv[B, (nq + 2 nkv) * dh] (q heads, k heads, v heads):
+ *                       per-head RMSNorm of q and k with q_norm / k_norm [dh]
+ *                       (NULL: none), rotary embedding with cos / sin tables
+ *                       [S, dh] (halves duplicated) at position *pos (device
+ *                       int64); q -> q_out[B, nq, dh], k and v -> the caches
+ *                       [B, nkv, S, dh] at row *pos
+ *   rdq_attn_decode     out[B, nq * dh] = softmax(q K^T * scale) V over cache
+ *                       rows 0 .. *pos, grouped-query (nq % nkv == 0), positions
+ *                       split over CTAs and merged by a second small kernel;
+ *                       scratch: rdq_attn_decode_scratch_size bytes (f32)
+ *   rdq_silu_mul        out[B,F] = silu(gate_up[B, 0:F]) * gate_up[B, F:2F]
+ */
+int rdq_add_rmsnorm(void *x, const void *delta, const void *weight, void *out,
+                    int B, int H, float eps, int flags, void *stream);
+int rdq_qk_rope_cache(const void *qkv, const void *q_norm, const void *k_norm,
+                      const void *cos_table, const void *sin_table,
+                      const long long *pos, void *q_out, void *k_cache,
+                      void *v_cache, int B, int n_q_heads, int n_kv_heads,
+                      int head_dim, int S, float eps, int flags, void *stream);
+int rdq_attn_decode_scratch_size(int B, int n_q_heads, int head_dim, int S,
+                                 size_t *bytes);
+int rdq_attn_decode(const void *q, const void *k_cache, const void *v_cache,
+                    const long long *pos, void *scratch, void *out, int B,
+                    int n_q_heads, int n_kv_heads, int head_dim, int S,
+                    float scale, int flags, void *stream);
+int rdq_silu_mul(const void *gate_up, void *out, int B, int F, int flags,
+                 void *stream);
+
+/*
  * Copy `bytes` bytes between device-accessible buffers with a small kernel
  * rather than the copy engine: meant for the few KB of activations / results a
  * decode step moves between pinned (mapped) host memory and device memory

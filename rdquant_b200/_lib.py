@@ -22,6 +22,7 @@ SOURCES = [
     "rdq_gemm.cu",
     "rdq_quantize.cu",
     "rdq_stage.cu",
+    "rdq_glue.cu",
 ]
 HEADERS = ["rdq_common.cuh", "rdq_kernels.cuh", "rdq_gemv_tiled_kernel.inl", "rdq_gemm_kernel.inl",
            os.path.join("..", "..", "include", "rdq_b200.h")]
@@ -107,6 +108,16 @@ def _bind(lib: ctypes.CDLL) -> None:
     lib.rdq_quantize_nvfp4.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp]
     lib.rdq_quantize_fp8.restype = i32
     lib.rdq_quantize_fp8.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp]
+    lib.rdq_add_rmsnorm.restype = i32
+    lib.rdq_add_rmsnorm.argtypes = [vp, vp, vp, vp, i32, i32, f32, i32, vp]
+    lib.rdq_qk_rope_cache.restype = i32
+    lib.rdq_qk_rope_cache.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp]
+    lib.rdq_attn_decode_scratch_size.restype = i32
+    lib.rdq_attn_decode_scratch_size.argtypes = [i32, i32, i32, i32, ctypes.POINTER(ctypes.c_size_t)]
+    lib.rdq_attn_decode.restype = i32
+    lib.rdq_attn_decode.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp]
+    lib.rdq_silu_mul.restype = i32
+    lib.rdq_silu_mul.argtypes = [vp, vp, i32, i32, i32, vp]
     lib.rdq_stage_copy.restype = i32
     lib.rdq_stage_copy.argtypes = [vp, vp, ctypes.c_size_t, vp]
 
@@ -131,6 +142,11 @@ EXPORTS = [
     "rdq_quantize_nvfp4",
     "rdq_quantize_fp8",
     "rdq_stage_copy",
+    "rdq_add_rmsnorm",
+    "rdq_qk_rope_cache",
+    "rdq_attn_decode_scratch_size",
+    "rdq_attn_decode",
+    "rdq_silu_mul",
 ]
 
 

@@ -284,6 +284,63 @@ int rdq_quantize_fp8(const void *w, int w_is_f32, int n, int K, void *out, float
                              static_cast<cudaStream_t>(stream));
 }
 
+int rdq_add_rmsnorm(void *x, const void *delta, const void *weight, void *out, int B, int H, float eps, int flags,
+                    void *stream) {
+  RDQ_REQUIRE(B >= 0 && H > 0 && H % 8 == 0, RDQ_E_INVALID, "rdq_add_rmsnorm needs H a positive multiple of 8 (B=%d H=%d)", B, H);
+  if (B == 0) return RDQ_OK;
+  RDQ_REQUIRE(x && weight && out, RDQ_E_INVALID, "x, weight and out must not be null");
+  RDQ_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(out) && aligned16(delta), RDQ_E_INVALID,
+              "x, delta, weight and out must be 16-byte aligned");
+  return launch_add_rmsnorm(static_cast<__half *>(x), static_cast<const __half *>(delta), static_cast<const __half *>(weight),
+                            static_cast<__half *>(out), B, H, eps, (flags & RDQ_GEMV_PDL) != 0, static_cast<cudaStream_t>(stream));
+}
+
+int rdq_qk_rope_cache(const void *qkv, const void *q_norm, const void *k_norm, const void *cos_table, const void *sin_table,
+                      const long long *pos, void *q_out, void *k_cache, void *v_cache, int B, int n_q_heads, int n_kv_heads,
+                      int head_dim, int S, float eps, int flags, void *stream) {
+  RDQ_REQUIRE(B >= 0 && n_q_heads > 0 && n_kv_heads > 0 && S > 0, RDQ_E_INVALID, "bad attention geometry");
+  RDQ_REQUIRE(head_dim >= 64 && head_dim <= 256 && head_dim % 64 == 0, RDQ_E_UNSUPPORTED,
+              "head_dim must be 64, 128, 192 or 256, got %d", head_dim);
+  if (B == 0) return RDQ_OK;
+  RDQ_REQUIRE(qkv && cos_table && sin_table && pos && q_out && k_cache && v_cache, RDQ_E_INVALID, "null pointer");
+  return launch_qk_rope_cache(static_cast<const __half *>(qkv), static_cast<const __half *>(q_norm),
+                              static_cast<const __half *>(k_norm), static_cast<const __half *>(cos_table),
+                              static_cast<const __half *>(sin_table), pos, static_cast<__half *>(q_out),
+                              static_cast<__half *>(k_cache), static_cast<__half *>(v_cache), B, n_q_heads, n_kv_heads, head_dim,
+                              S, eps, (flags & RDQ_GEMV_PDL) != 0, static_cast<cudaStream_t>(stream));
+}
+
+int rdq_attn_decode_scratch_size(int B, int n_q_heads, int head_dim, int S, size_t *bytes) {
+  RDQ_REQUIRE(bytes && B >= 0 && n_q_heads > 0 && head_dim > 0 && S > 0, RDQ_E_INVALID, "bad arguments");
+  const int nsplit = (S + attn_chunk() - 1) / attn_chunk();
+  *bytes = sizeof(float) * static_cast<size_t>(B) * n_q_heads * nsplit * (head_dim + 2);
+  return RDQ_OK;
+}
+
+int rdq_attn_decode(const void *q, const void *k_cache, const void *v_cache, const long long *pos, void *scratch, void *out,
+                    int B, int n_q_heads, int n_kv_heads, int head_dim, int S, float scale, int flags, void *stream) {
+  RDQ_REQUIRE(B >= 0 && n_q_heads > 0 && n_kv_heads > 0 && n_q_heads % n_kv_heads == 0 && S > 0, RDQ_E_INVALID,
+              "bad attention geometry");
+  RDQ_REQUIRE(head_dim >= 32 && head_dim <= 256 && head_dim % 32 == 0, RDQ_E_UNSUPPORTED,
+              "head_dim must be a multiple of 32 up to 256, got %d", head_dim);
+  if (B == 0) return RDQ_OK;
+  RDQ_REQUIRE(q && k_cache && v_cache && pos && scratch && out, RDQ_E_INVALID, "null pointer");
+  RDQ_REQUIRE((reinterpret_cast<uintptr_t>(k_cache) & 7) == 0 && (reinterpret_cast<uintptr_t>(v_cache) & 7) == 0, RDQ_E_INVALID,
+              "caches must be 8-byte aligned");
+  return launch_attn_decode(static_cast<const __half *>(q), static_cast<const __half *>(k_cache),
+                            static_cast<const __half *>(v_cache), pos, static_cast<float *>(scratch), static_cast<__half *>(out),
+                            B, n_q_heads, n_kv_heads, head_dim, S, scale, (flags & RDQ_GEMV_PDL) != 0,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int rdq_silu_mul(const void *gate_up, void *out, int B, int F, int flags, void *stream) {
+  RDQ_REQUIRE(B >= 0 && F > 0 && F % 8 == 0, RDQ_E_INVALID, "rdq_silu_mul needs F a positive multiple of 8 (B=%d F=%d)", B, F);
+  if (B == 0) return RDQ_OK;
+  RDQ_REQUIRE(gate_up && out && aligned16(gate_up) && aligned16(out), RDQ_E_INVALID, "gate_up and out must be 16-byte aligned");
+  return launch_silu_mul(static_cast<const __half *>(gate_up), static_cast<__half *>(out), B, F, (flags & RDQ_GEMV_PDL) != 0,
+                         static_cast<cudaStream_t>(stream));
+}
+
 int rdq_stage_copy(void *dst, const void *src, size_t bytes, void *stream) {
   RDQ_REQUIRE(bytes == 0 || (dst != nullptr && src != nullptr), RDQ_E_INVALID, "dst and src must not be null");
   RDQ_REQUIRE(aligned16(dst) && aligned16(src), RDQ_E_INVALID, "dst and src must be 16-byte aligned");

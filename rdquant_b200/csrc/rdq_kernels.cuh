@@ -92,6 +92,17 @@ size_t gemm_workspace_bytes(int M, int N, int K);
 // staging copy by kernel (rdq_stage.cu)
 int launch_stage_copy(void *dst, const void *src, size_t bytes, cudaStream_t stream);
 
+// decode-step glue (rdq_glue.cu)
+int launch_add_rmsnorm(__half *x, const __half *delta, const __half *w, __half *out, int B, int H, float eps, bool pdl,
+                       cudaStream_t stream);
+int launch_qk_rope_cache(const __half *qkv, const __half *qn, const __half *kn, const __half *cos_t, const __half *sin_t,
+                         const long long *pos, __half *q_out, __half *k_cache, __half *v_cache, int B, int nq, int nkv,
+                         int dh, int S, float eps, bool pdl, cudaStream_t stream);
+int attn_chunk();
+int launch_attn_decode(const __half *q, const __half *k_cache, const __half *v_cache, const long long *pos, float *scratch,
+                       __half *out, int B, int nq, int nkv, int dh, int S, float scale, bool pdl, cudaStream_t stream);
+int launch_silu_mul(const __half *gu, __half *out, int B, int F, bool pdl, cudaStream_t stream);
+
 // encoders (rdq_quantize.cu)
 int launch_quantize_nvfp4(const void *w, bool w_is_f32, int n, int K, uint8_t *codes, uint8_t *scales, float *row_sqerr,
                           float *max_scale, cudaStream_t stream);

@@ -2,10 +2,13 @@
 prefill / greedy-decode measurements on synthetic weights (BASELINE configs 4 and 5; the
 reference's harness is benchmarks/bench_e2e.py:103-155 over a HuggingFace model).
 
-Everything that is not a linear layer -- embedding lookup, RMSNorm, rotary embedding, the
-attention over the KV cache, SiLU x mul, the residual adds, the FP16 lm_head and the arg-max --
-is plain PyTorch: it is glue around the operator this package provides, not part of it.  q/k/v
-and gate/up are packed as one layer each (they read the same input).  A decode step has static
+q/k/v and gate/up are packed as one layer each (they read the same input).  In the prefill pass
+everything that is not a linear layer -- embedding lookup, RMSNorm, rotary embedding, attention,
+SiLU x mul, residual adds -- is plain PyTorch.  A decode step uses the glue kernels of
+csrc/rdq_glue.cu instead (residual add + RMSNorm, q/k norm + rotary + cache write, single-token
+attention, SiLU x mul: 9 launches per block, all chained by programmatic dependent launch with the
+GEMVs), or, with ``fused_glue=False``, the same PyTorch operators as the prefill; the embedding
+lookup, the FP16 lm_head and the arg-max are PyTorch in both.  A decode step has static
 shapes (the KV cache is allocated for the whole run, the current position lives in a device
 tensor), so it is captured once in a CUDA graph and replayed per token.
 
@@ -73,9 +76,10 @@ class MixedDecoder:
     """Random-init decoder; weights are generated, encoded and packed layer by layer on the GPU."""
 
     def __init__(self, cfg: DecoderConfig, device, max_seq: int, batch: int, seed: int = 0, rank: int = 0,
-                 world: int = 1, group=None, use_pdl: bool = True) -> None:
+                 world: int = 1, group=None, use_pdl: bool = True, fused_glue: bool = True) -> None:
         self.cfg, self.device, self.max_seq, self.batch = cfg, torch.device(device), max_seq, batch
         self.rank, self.world, self.group = rank, world, group
+        self.use_pdl, self.fused_glue = use_pdl, fused_glue
         gen = torch.Generator(device=self.device).manual_seed(seed)
         h, dh = cfg.hidden, cfg.head_dim
         nq, nkv = cfg.q_heads * dh, cfg.kv_heads * dh
@@ -114,6 +118,15 @@ class MixedDecoder:
             blk["v"] = torch.zeros(batch, cfg.kv_heads, self.max_seq, cfg.head_dim, dtype=torch.float16, device=self.device)
         self.pos = torch.zeros(1, dtype=torch.long, device=self.device)      # next position to write
         self.ids = torch.zeros(batch, dtype=torch.long, device=self.device)  # tokens fed to the next step
+        from rdquant_b200 import rdquant_cuda
+
+        f16 = dict(dtype=torch.float16, device=self.device)
+        self._bufs = {
+            "x": torch.zeros(batch, cfg.hidden, **f16), "h": torch.zeros(batch, cfg.hidden, **f16),
+            "q": torch.zeros(batch, cfg.q_heads, cfg.head_dim, **f16),
+            "att": torch.zeros(batch, cfg.q_heads * cfg.head_dim, **f16), "act": torch.zeros(batch, cfg.ffn, **f16),
+            "scratch": rdquant_cuda.attn_decode_scratch(batch, cfg.q_heads, cfg.head_dim, self.max_seq, self.device),
+        }
 
     # ---- construction
     def _linear(self, shapes, gen, use_pdl):
@@ -187,8 +200,34 @@ class MixedDecoder:
         self.ids.copy_(logits.argmax(-1))
         return self.ids.clone()
 
+    def _forward_fused(self) -> torch.Tensor:
+        """One decode step (one token per sequence) with the glue kernels of rdq_glue.cu between
+        the linears instead of framework operators: 9 launches per block."""
+        from rdquant_b200 import _lib, rdquant_cuda as rc
+
+        cfg, st = self.cfg, self._bufs
+        flags = _lib.RDQ_GEMV_PDL if self.use_pdl else 0
+        x, hbuf = st["x"], st["h"]
+        torch.index_select(self.embed, 0, self.ids, out=x)
+        delta = None
+        scale = cfg.head_dim ** -0.5
+        for blk in self.blocks:
+            rc.add_rmsnorm(x, delta, blk["ln1"], hbuf, cfg.eps, flags)
+            qkv = blk["qkv"](hbuf)
+            rc.qk_rope_cache(qkv, blk["qn"] if cfg.qk_norm else None, blk["kn"] if cfg.qk_norm else None, self.cos, self.sin,
+                             self.pos, st["q"], blk["k"], blk["v"], cfg.eps, flags)
+            rc.attn_decode(st["q"], blk["k"], blk["v"], self.pos, st["scratch"], st["att"], scale, flags)
+            rc.add_rmsnorm(x, blk["o"](st["att"]), blk["ln2"], hbuf, cfg.eps, flags)
+            rc.silu_mul(blk["gate_up"](hbuf), st["act"], flags)
+            delta = blk["down"](st["act"])
+        rc.add_rmsnorm(x, delta, self.norm, hbuf, cfg.eps, flags)
+        return hbuf @ self.lm_head.T
+
     def _step(self) -> None:
-        logits = self._forward(self.ids[:, None], 1, self.pos)
+        if self.fused_glue:
+            logits = self._forward_fused()
+        else:
+            logits = self._forward(self.ids[:, None], 1, self.pos)
         self.ids.copy_(logits.argmax(-1))
         self.pos.add_(1)
 

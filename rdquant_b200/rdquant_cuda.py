@@ -380,3 +380,84 @@ def stage_copy(dst: torch.Tensor, src: torch.Tensor) -> None:
         raise RuntimeError("stage_copy: size mismatch")
     with _on_device(dev_t.device):
         _lib.check(_lib.lib().rdq_stage_copy(_ptr(dst), _ptr(src), nbytes, _stream(dev_t.device)), "rdq_stage_copy")
+
+
+# ---- decode-step glue (rdq_glue.cu): thin wrappers, all tensors preallocated by the caller
+
+def _need_f16(name: str, t: torch.Tensor) -> None:
+    _need_cuda(name, t, torch.float16)
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
+                eps: float, flags: int = 0) -> torch.Tensor:
+    """``x += delta`` (in place; ``delta`` may be None) and ``out = rmsnorm(x) * weight``; x, out ``[B, H]``."""
+    for name, t in (("x", x), ("weight", weight), ("out", out)):
+        _need_f16(name, t)
+    if delta is not None:
+        _need_f16("delta", delta)
+        if delta.shape != x.shape:
+            raise RuntimeError("delta must have the shape of x")
+    b, h = x.shape
+    if out.shape != x.shape or weight.numel() != h:
+        raise RuntimeError("add_rmsnorm: shape mismatch")
+    with _on_device(x.device):
+        rc = _lib.lib().rdq_add_rmsnorm(_ptr(x), _ptr(delta), _ptr(weight), _ptr(out), b, h, float(eps), int(flags),
+                                        _stream(x.device))
+    _lib.check(rc, "rdq_add_rmsnorm")
+    return out
+
+
+def qk_rope_cache(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], cos: torch.Tensor,
+                  sin: torch.Tensor, pos: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                  eps: float, flags: int = 0) -> None:
+    """Per-head q/k RMSNorm (optional) + rotary embedding at position ``pos`` (int64 device scalar);
+    q -> ``q_out [B, nq, dh]``, k / v -> ``k_cache`` / ``v_cache [B, nkv, S, dh]`` row ``pos``."""
+    for name, t in (("qkv", qkv), ("cos", cos), ("sin", sin), ("q_out", q_out), ("k_cache", k_cache), ("v_cache", v_cache)):
+        _need_f16(name, t)
+    _need_cuda("pos", pos, torch.int64)
+    b, nq, dh = q_out.shape
+    _, nkv, s, _ = k_cache.shape
+    if qkv.shape != (b, (nq + 2 * nkv) * dh) or v_cache.shape != k_cache.shape or cos.shape != (s, dh) or sin.shape != (s, dh):
+        raise RuntimeError("qk_rope_cache: shape mismatch")
+    with _on_device(qkv.device):
+        rc = _lib.lib().rdq_qk_rope_cache(_ptr(qkv), _ptr(q_norm), _ptr(k_norm), _ptr(cos), _ptr(sin), _ptr(pos), _ptr(q_out),
+                                          _ptr(k_cache), _ptr(v_cache), b, nq, nkv, dh, s, float(eps), int(flags),
+                                          _stream(qkv.device))
+    _lib.check(rc, "rdq_qk_rope_cache")
+
+
+def attn_decode_scratch(b: int, nq: int, dh: int, s: int, device) -> torch.Tensor:
+    need = ctypes.c_size_t(0)
+    _lib.check(_lib.lib().rdq_attn_decode_scratch_size(b, nq, dh, s, ctypes.byref(need)), "rdq_attn_decode_scratch_size")
+    return torch.empty(max(need.value // 4, 1), dtype=torch.float32, device=device)
+
+
+def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor, scratch: torch.Tensor,
+                out: torch.Tensor, scale: float, flags: int = 0) -> torch.Tensor:
+    """``out [B, nq * dh] = softmax(q K^T * scale) V`` over cache rows ``0 .. pos`` (grouped-query)."""
+    for name, t in (("q", q), ("k_cache", k_cache), ("v_cache", v_cache), ("out", out)):
+        _need_f16(name, t)
+    _need_cuda("pos", pos, torch.int64)
+    _need_cuda("scratch", scratch, torch.float32)
+    b, nq, dh = q.shape
+    _, nkv, s, _ = k_cache.shape
+    if out.shape != (b, nq * dh):
+        raise RuntimeError("attn_decode: out must be [B, nq * dh]")
+    with _on_device(q.device):
+        rc = _lib.lib().rdq_attn_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(pos), _ptr(scratch), _ptr(out), b, nq, nkv,
+                                        dh, s, float(scale), int(flags), _stream(q.device))
+    _lib.check(rc, "rdq_attn_decode")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, flags: int = 0) -> torch.Tensor:
+    """``out [B, F] = silu(gate_up[:, :F]) * gate_up[:, F:]``."""
+    _need_f16("gate_up", gate_up)
+    _need_f16("out", out)
+    b, f = out.shape
+    if gate_up.shape != (b, 2 * f):
+        raise RuntimeError("silu_mul: gate_up must be [B, 2 F]")
+    with _on_device(out.device):
+        rc = _lib.lib().rdq_silu_mul(_ptr(gate_up), _ptr(out), b, f, int(flags), _stream(out.device))
+    _lib.check(rc, "rdq_silu_mul")
+    return out

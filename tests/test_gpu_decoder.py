@@ -32,6 +32,24 @@ def test_graph_replay_matches_eager_decode():
     assert int(model.pos) == 26
 
 
+def test_fused_glue_step_matches_framework_step():
+    """The decode step over the glue kernels gives the logits of the step over PyTorch operators."""
+    model = MixedDecoder(TINY, "cuda", max_seq=64, batch=3, seed=5)
+    ids = torch.randint(0, TINY.vocab, (3, 17), generator=torch.Generator().manual_seed(3)).cuda()
+    model.prefill(ids)
+    caches = [(b["k"].clone(), b["v"].clone()) for b in model.blocks]
+    with torch.no_grad():
+        ref = model._forward(model.ids[:, None], 1, model.pos).float()
+        for b, (k, v) in zip(model.blocks, caches):
+            b["k"].copy_(k)
+            b["v"].copy_(v)
+        got = model._forward_fused().float()
+    err = (got - ref).abs().max() / ref.abs().max()
+    assert float(err) < 1e-2, float(err)
+    for b in model.blocks:  # both paths wrote the same cache rows
+        assert float((b["k"][:, :, 17].float() - b["k"][:, :, 17].float()).abs().max()) == 0.0
+
+
 def test_prefill_and_decode_paths_agree():
     """Feeding the prompt token by token through the decode path (GEMV, M = 1) ends in the same
     logits as one prefill pass (GEMM, M = 20)."""

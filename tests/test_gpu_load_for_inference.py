@@ -75,7 +75,7 @@ def test_loaded_model_matches_dense_dequantised_model(tmp_path):
     # the same architecture with dense linears holding the bit-exact dequantised weights
     qcfg, tensors = hf_export.read_layers(str(tmp_path))
     dense = AutoModelForCausalLM.from_config(_tiny_config())
-    state = {k: v for k, v in tensors.items() if k in dict(dense.named_parameters()) or k in dict(dense.named_buffers())}
+    state = {k: v for k, v in tensors.items() if k in dense.state_dict()}  # (rotary tables are rebuilt from the config)
     for name in names:
         lconf = qcfg["layers"][name]
         data = {k[len(name) + 1:]: v.cuda() for k, v in tensors.items() if k.startswith(name + ".")}
