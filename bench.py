@@ -356,9 +356,14 @@ def decode_section(device, batches=(1, 8), prompt: int = 512, new_tokens: int = 
             # share of a token's time the linears alone would take at the block benchmark's rate
             res["linear_only_fraction"] = gemv_block_ms * cfg.layers / res["ms_per_token"]
         out["batch"][str(b)] = res
+        model.release_graph()
     del model
     torch.cuda.empty_cache()
     return out
+
+
+def _note(rank: int, msg: str) -> None:
+    print(f"[bench rank {rank} {time.strftime('%H:%M:%S')}] {msg}", file=sys.stderr, flush=True)
 
 
 def run_sharded(args, device, rank: int, world: int) -> None:
@@ -391,14 +396,18 @@ def run_sharded(args, device, rank: int, world: int) -> None:
 
     def gathers_only(i: int) -> None:
         for mod in mods[i % copies]:
-            send, buf, idx = mod._buffers(m)
+            send, buf, idx = mod._io_buffers(m)
             gather_outputs(send, mod.plan, mod.group, buffer=buf, index=idx)
 
     sampler = ClockSampler(device.index or 0)
     sampler.start()
-    for i in range(warmup):
+    _note(rank, "modules built")
+    # every weight copy runs once before anything is captured: the first call of a module
+    # allocates its buffers and copies its index table to the device
+    for i in range(max(warmup, copies)):
         one_step(i)
     torch.cuda.synchronize()
+    _note(rank, "warm-up done")
     # parity: the gathered outputs of one step against the CPU oracle on the whole layers
     from oracle import oracle_np as onp
 
@@ -421,6 +430,7 @@ def run_sharded(args, device, rank: int, world: int) -> None:
         for mod in row:
             rdquant_cuda.check_status(mod.fd)
 
+    _note(rank, "parity checked")
     stream = torch.cuda.Stream(device)
     graph, ggraph = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
     replays = 10
@@ -428,16 +438,18 @@ def run_sharded(args, device, rank: int, world: int) -> None:
         one_step(0)
         gathers_only(0)
         stream.synchronize()
+        _note(rank, "capturing")
         with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
             for i in range(steps):
                 one_step(i)
         with torch.cuda.graph(ggraph, stream=stream, capture_error_mode="thread_local"):
             for i in range(steps):
                 gathers_only(i)
-        t_spin = time.time()
-        while time.time() - t_spin < 0.3:
+        _note(rank, "captured")
+        for _ in range(20):  # a fixed count: every rank must issue the same collectives
             graph.replay()
-            stream.synchronize()
+        stream.synchronize()
+        _note(rank, "graph warm")
         dist.barrier()
         torch.cuda.synchronize()
         t0 = time.time()
@@ -446,6 +458,7 @@ def run_sharded(args, device, rank: int, world: int) -> None:
         dist.barrier()
         gtimes = time_replays(ggraph, stream, 5)
     clocks = sampler.stop(t0, t1)
+    _note(rank, "timed")
 
     # ---- end to end: host activations in, host results out, synchronised every step
     x_host = [x.clone().pin_memory() for x in xs_cpu]
@@ -466,6 +479,7 @@ def run_sharded(args, device, rank: int, world: int) -> None:
         e2e_step(i)
     te = time.perf_counter() - te0
 
+    _note(rank, "e2e done")
     t = torch.tensor([statistics.median(times), min(times), max(times), statistics.median(gtimes), te],
                      dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -518,6 +532,7 @@ def run_sharded(args, device, rank: int, world: int) -> None:
         "clocks": clocks,
         "cpu_baseline": None,
     }
+    del graph, ggraph  # graphs that captured collectives must go before the process group does
     if args.decode:
         line["decode"] = decode_section(device, batches=(1,), rank=rank, world=world)
     if rank == 0:
@@ -561,13 +576,20 @@ def main() -> None:
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-        try:
-            run_sharded(args, device, rank, world)
-        finally:
-            dist.barrier()
-            dist.destroy_process_group()
-        return
+        import datetime
+        import faulthandler
+
+        # a rank that stops answering must end the run with a message, not hang it
+        faulthandler.dump_traceback_later(240, exit=True)
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
+        run_sharded(args, device, rank, world)
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        # Tearing the NCCL communicator down after its collectives were captured in CUDA graphs was
+        # seen to block (torch 2.11, NCCL 2.28): every rank has printed and synchronised, leave.
+        os._exit(0)
 
     steps, warmup, m = max(args.steps, 1), max(args.warmup, 3), args.m
     copies = max(args.copies, 2)

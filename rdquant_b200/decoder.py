@@ -248,6 +248,10 @@ class MixedDecoder:
         self.pos.copy_(pos_saved)
         self.ids.copy_(ids_saved)
 
+    def release_graph(self) -> None:
+        """Drop the captured step (before a process group whose collectives it holds goes away)."""
+        self._graph = None
+
     @torch.no_grad()
     def decode_step(self) -> None:
         if self._graph is None:

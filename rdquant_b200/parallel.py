@@ -174,7 +174,7 @@ class ColumnParallelMixedLinear(nn.Module):
         self.use_pdl = False
         self._state: dict = {}
 
-    def _buffers(self, m: int):
+    def _io_buffers(self, m: int):
         st = self._state.get(m)
         if st is None:
             send = torch.zeros(m, self.plan.n_max, dtype=torch.float16, device=self.device)
@@ -194,7 +194,7 @@ class ColumnParallelMixedLinear(nn.Module):
         x2 = x.reshape(-1, self.K)
         xh = (x2 if x2.dtype == torch.float16 else x2.half()).contiguous()
         m = xh.shape[0]
-        send, buf, idx = self._buffers(m)
+        send, buf, idx = self._io_buffers(m)
         flags = _lib.RDQ_GEMV_PDL if self.use_pdl else 0
         rdquant_cuda.mixed_linear(xh, self.fd, self.bias_local, flags, out=send)
         if not self.gather:
