@@ -309,7 +309,7 @@ def prefill_section(device, units, tokens=(512, 2048, 8192), steps: int = 10) ->
 
 
 def decode_section(device, batches=(1, 8), prompt: int = 512, new_tokens: int = 256, cfg=None, rank=0, world=1,
-                   gemv_block_ms=None) -> dict:
+                   gemv_block_ms=None, peer=True) -> dict:
     """Whole-model greedy decoding (BASELINE configs[3]): random-init Qwen3-4B-shaped stack, all
     linears mixed-precision, `prompt`-token prefill through the GEMM, then `new_tokens` tokens, one
     CUDA-graph replay per token.  tokens/s = batch * new_tokens / device time of the decode loop."""
@@ -320,8 +320,12 @@ def decode_section(device, batches=(1, 8), prompt: int = 512, new_tokens: int = 
 
     cfg = cfg or QWEN3_4B
     out = {"model": cfg.name, "layers": cfg.layers, "prompt_tokens": prompt, "new_tokens": new_tokens, "batch": {}}
+    if world > 1:
+        out["parallelism"] = f"column-parallel x{world}, " + ("all-gather fused into the GEMV epilogue (peer stores)"
+                                                               if peer else "NCCL all-gather per linear")
     t_build = time.time()
-    model = MixedDecoder(cfg, device, max_seq=prompt + new_tokens + 8, batch=batches[0], seed=7, rank=rank, world=world)
+    model = MixedDecoder(cfg, device, max_seq=prompt + new_tokens + 8, batch=batches[0], seed=7, rank=rank, world=world,
+                         peer_gather=peer)
     torch.cuda.synchronize()
     t_build = time.time() - t_build
     for b in batches:
@@ -329,6 +333,9 @@ def decode_section(device, batches=(1, 8), prompt: int = 512, new_tokens: int = 
         gen = torch.Generator().manual_seed(11)
         ids = torch.randint(0, cfg.vocab, (b, prompt), generator=gen).to(device)
         e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        if b == batches[0]:
+            model.prefill(ids[:, :64])  # untimed: library initialisation, kernel selection, allocations
+            model.reset(b)
         if world > 1:
             dist.barrier()
         e0.record()
@@ -372,16 +379,23 @@ def run_sharded(args, device, rank: int, world: int) -> None:
     import torch.distributed as dist
 
     from rdquant_b200 import rdquant_cuda
-    from rdquant_b200.parallel import ColumnParallelMixedLinear, gather_outputs
+    from rdquant_b200.parallel import ColumnParallelMixedLinear, PeerArena, PeerGatherMixedLinear, gather_outputs
 
     steps, warmup, m = max(args.steps, 1), max(args.warmup, 3), args.m
+    peer = args.collective == "peer"
     per_layer = block_layers(device, seed=0)  # the same block on every rank
     units = fused_units(per_layer, fuse=not args.no_fuse)
     step_bytes = sum(u["bytes"] for u in units)
     # every rank streams 1/world of the block per step: rotate enough copies to exceed 2 x L2
     copies = max(args.copies, int(2 * L2_BYTES * world / step_bytes) + 1)
-    mods = [[ColumnParallelMixedLinear({kk: v.clone() for kk, v in u["data"].items()}, u["splits"], u["k"], device,
-                                       rank, world) for u in units] for _ in range(copies)]
+    if peer:
+        widest = max(u["n"] for u in units)
+        arena = PeerArena(copies * len(units) * ((widest // world + 256) * world * 16 * 2 + 1024), device)
+        mods = [[PeerGatherMixedLinear({kk: v.clone() for kk, v in u["data"].items()}, u["splits"], u["k"], arena)
+                 for u in units] for _ in range(copies)]
+    else:
+        mods = [[ColumnParallelMixedLinear({kk: v.clone() for kk, v in u["data"].items()}, u["splits"], u["k"], device,
+                                           rank, world) for u in units] for _ in range(copies)]
     for row in mods:
         for mod in row:
             mod.use_pdl = not args.no_pdl
@@ -395,6 +409,8 @@ def run_sharded(args, device, rank: int, world: int) -> None:
             ys[li] = mod(xs[li])
 
     def gathers_only(i: int) -> None:
+        if peer:
+            return
         for mod in mods[i % copies]:
             send, buf, idx = mod._io_buffers(m)
             gather_outputs(send, mod.plan, mod.group, buffer=buf, index=idx)
@@ -426,10 +442,15 @@ def run_sharded(args, device, rank: int, world: int) -> None:
         dist.all_reduce(hi, op=dist.ReduceOp.MAX)
         if float(hi - lo) != 0.0:
             raise RuntimeError("ranks disagree on the gathered output of layer %d" % li)
-    for row in mods:
-        for mod in row:
-            rdquant_cuda.check_status(mod.fd)
+    def check_all() -> None:
+        for row in mods:
+            for mod in row:
+                if peer:
+                    mod.check_status()
+                else:
+                    rdquant_cuda.check_status(mod.fd)
 
+    check_all()
     _note(rank, "parity checked")
     stream = torch.cuda.Stream(device)
     graph, ggraph = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
@@ -442,9 +463,10 @@ def run_sharded(args, device, rank: int, world: int) -> None:
         with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
             for i in range(steps):
                 one_step(i)
-        with torch.cuda.graph(ggraph, stream=stream, capture_error_mode="thread_local"):
-            for i in range(steps):
-                gathers_only(i)
+        if not peer:
+            with torch.cuda.graph(ggraph, stream=stream, capture_error_mode="thread_local"):
+                for i in range(steps):
+                    gathers_only(i)
         _note(rank, "captured")
         for _ in range(20):  # a fixed count: every rank must issue the same collectives
             graph.replay()
@@ -456,8 +478,9 @@ def run_sharded(args, device, rank: int, world: int) -> None:
         times = time_replays(graph, stream, replays)
         t1 = time.time()
         dist.barrier()
-        gtimes = time_replays(ggraph, stream, 5)
+        gtimes = time_replays(ggraph, stream, 5) if not peer else [0.0]
     clocks = sampler.stop(t0, t1)
+    check_all()
     _note(rank, "timed")
 
     # ---- end to end: host activations in, host results out, synchronised every step
@@ -507,7 +530,10 @@ def run_sharded(args, device, rank: int, world: int) -> None:
             "bytes_per_step": step_bytes,
             "parallelism": f"column-parallel x{world}: every format group of every layer cut at 128-channel "
                            "boundaries, x replicated, outputs all-gathered and un-permuted on every rank",
-            "collective": f"all_gather_into_tensor x{len(units)} per step (NCCL, inside the timed CUDA graph)",
+            "collective": (f"fused into the GEMV epilogue: each rank stores its slice into every GPU's gather buffer "
+                           f"over NVLink (peer memory), flag + bounded wait + un-permute kernel; x{len(units)} per step, "
+                           "inside the timed CUDA graph, no NCCL call") if peer else
+                          f"all_gather_into_tensor x{len(units)} per step (NCCL, inside the timed CUDA graph)",
             "l2_policy": f"{copies} rotating weight copies = {copies * step_bytes / world / 1e6:.0f} MB per rank "
                          "> 2 x L2; no flush",
             "launch": "one CUDA graph of all timed steps; median of %d replays" % replays,
@@ -516,7 +542,7 @@ def run_sharded(args, device, rank: int, world: int) -> None:
         "gpu_launches": launches,
         "timing": {"replays": replays, "ms_per_step_median": ms / steps, "ms_per_step_min": ms_min / steps,
                    "ms_per_step_max": ms_max / steps},
-        "collective_ms_per_step": gms / steps,
+        "collective_ms_per_step": None if peer else gms / steps,
         "parity_max_rel_err": parity,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peak_kind,
@@ -527,14 +553,15 @@ def run_sharded(args, device, rank: int, world: int) -> None:
                 "h2d_bytes_per_step": sum(2 * m * u["k"] for u in units),
                 "d2h_bytes_per_step": sum(2 * m * u["n"] for u in units), "steps": e2e_steps,
                 "ms_per_step": 1e3 * te / e2e_steps,
-                "api": "parallel.ColumnParallelMixedLinear.forward per layer: pinned host x -> device, fused GEMV + "
-                       "all-gather + un-permute, y -> pinned host, synchronised every step"},
+                "api": "parallel.%s.forward per layer: pinned host x -> device, fused GEMV + "
+                       "all-gather + un-permute, y -> pinned host, synchronised every step"
+                       % ("PeerGatherMixedLinear" if peer else "ColumnParallelMixedLinear")},
         "clocks": clocks,
         "cpu_baseline": None,
     }
     del graph, ggraph  # graphs that captured collectives must go before the process group does
     if args.decode:
-        line["decode"] = decode_section(device, batches=(1,), rank=rank, world=world)
+        line["decode"] = decode_section(device, batches=(1,), rank=rank, world=world, peer=peer)
     if rank == 0:
         print(json.dumps(line), flush=True)
 
@@ -554,6 +581,8 @@ def main() -> None:
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM section")
     ap.add_argument("--no-decode", dest="decode", action="store_false", help="skip whole-model decoding")
     ap.add_argument("--decode-batches", default="1,8", help="batch sizes of the whole-model decode section")
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: all-gather fused into the GEMV epilogue over peer memory, or NCCL")
     ap.set_defaults(decode=True)
     args = ap.parse_args()
 

@@ -166,6 +166,43 @@ int rdq_gemv_tiled(const void *x, int M,
                    int flags, void *stream);
 
 /*
+ * Column-parallel layers on the GPUs of one node (no counterpart in the
+ * reference, which is single-GPU): the tiled GEMV with the all-gather of the
+ * outputs fused into its epilogue.  Instead of y, the kernel stores its slice
+ * -- y_slice[m, p] for the rows p of this rank's shard, in the shard's row
+ * order -- into `n_dst` destinations: dst[d] is the place of this rank's slice
+ * inside the gather buffer of GPU d (peer memory reachable by plain stores over
+ * NVLink, e.g. symmetric memory; the local buffer is one of them).  When the
+ * last epilogue warp of the grid has finished, it stores the launch number into
+ * peer_flags[d] (this rank's flag word on GPU d) with release semantics.
+ * peer_state: two zero-initialised int32 on this GPU, owned by the layer
+ * ([0] warps done, [1] launches completed).  Everything else as rdq_gemv_tiled.
+ *
+ * rdq_peer_gather is the receiving side, one small kernel launched after the
+ * layer's rdq_gemv_tiled_peer on the same stream: it waits until the flag words
+ * flags[0 .. world) on this GPU all show the launch number that GEMV left in
+ * peer_state[1] (bounded: about wait_ms milliseconds, then *status = 10 + the
+ * rank that did not arrive and y is left untouched) and copies
+ * y[i] = buffer[index[i]] for i < count (un-permute out of the gather buffer).
+ * flags_pdl: RDQ_GEMV_PDL makes it take part in programmatic dependent launch.
+ * Both calls are plain kernel launches: a whole decode step can be captured in
+ * a CUDA graph.  No TMA or multicast access touches another GPU's memory.
+ */
+int rdq_gemv_tiled_peer(const void *x, int M,
+                        const void *w_tiled, const float *w_fp8_scales,
+                        float w_fp4_global_scale,
+                        const int32_t *perm, const void *bias,
+                        void *const *dst, int32_t *const *peer_flags, int n_dst,
+                        int32_t *peer_state,
+                        int n_fp4, int n_fp8, int n_fp16, int K,
+                        void *workspace, int32_t *counters,
+                        int flags, void *stream);
+int rdq_peer_gather(const void *buffer, const long long *index, void *y,
+                    long long count, const int32_t *flags, int world,
+                    const int32_t *peer_state, int32_t *status, int wait_ms,
+                    int flags_pdl, void *stream);
+
+/*
  * rdq_gemv_tiled for callers that cannot allocate device memory.  (No
  * counterpart in the reference.)  Some hosts of this library run where
  * cudaMalloc is off limits: serving loops that forbid allocation once they

@@ -88,6 +88,10 @@ def _bind(lib: ctypes.CDLL) -> None:
     lib.rdq_gemv_repack.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
     lib.rdq_gemv_tiled.restype = i32
     lib.rdq_gemv_tiled.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp]
+    lib.rdq_gemv_tiled_peer.restype = i32
+    lib.rdq_gemv_tiled_peer.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, vp, vp, i32, vp]
+    lib.rdq_peer_gather.restype = i32
+    lib.rdq_peer_gather.argtypes = [vp, vp, vp, ctypes.c_longlong, vp, i32, vp, vp, i32, i32, vp]
     lib.rdq_gemv_tiled_noalloc.restype = i32
     lib.rdq_gemv_tiled_noalloc.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, i32, i32, i32, i32, i32, vp]
     lib.rdq_gemv_tiled_status.restype = i32
@@ -132,6 +136,8 @@ EXPORTS = [
     "rdq_gemv_repack",
     "rdq_gemv_tiled",
     "rdq_gemv_tiled_noalloc",
+    "rdq_gemv_tiled_peer",
+    "rdq_peer_gather",
     "rdq_gemv_tiled_status",
     "rdq_gemv_tiled_noalloc_status",
     "rdq_gemm_status",

@@ -168,6 +168,53 @@ int rdq_gemv_tiled(const void *x, int M, const void *w_tiled, const float *w_fp8
   return launch_gemv_tiled(a, (flags & RDQ_GEMV_PDL) != 0, static_cast<cudaStream_t>(stream));
 }
 
+int rdq_gemv_tiled_peer(const void *x, int M, const void *w_tiled, const float *w_fp8_scales, float w_fp4_global_scale,
+                        const int32_t *perm, const void *bias, void *const *dst, int32_t *const *peer_flags, int n_dst,
+                        int32_t *peer_state, int n_fp4, int n_fp8, int n_fp16, int K, void *workspace, int32_t *counters,
+                        int flags, void *stream) {
+  RDQ_REQUIRE(n_fp4 >= 0 && n_fp8 >= 0 && n_fp16 >= 0 && K > 0, RDQ_E_INVALID, "bad layer shape");
+  RDQ_REQUIRE(M >= 1 && M <= RDQ_MAX_GEMV_M, RDQ_E_UNSUPPORTED, "rdq_gemv_tiled_peer takes 1..%d activation rows, got M=%d",
+              RDQ_MAX_GEMV_M, M);
+  RDQ_REQUIRE(n_dst >= 1 && n_dst <= kMaxPeers, RDQ_E_UNSUPPORTED, "1..%d destinations, got %d", kMaxPeers, n_dst);
+  RDQ_REQUIRE(tiled_supported(n_fp4, n_fp8, n_fp16, K), RDQ_E_UNSUPPORTED, "shape has no tiled layout (K=%d, n=%d/%d/%d)", K,
+              n_fp4, n_fp8, n_fp16);
+  RDQ_REQUIRE(x && w_tiled && workspace && counters && dst && peer_flags && peer_state, RDQ_E_INVALID, "null pointer");
+  RDQ_REQUIRE(aligned16(x) && aligned16(w_tiled), RDQ_E_INVALID, "x and w_tiled must be 16-byte aligned");
+  RDQ_REQUIRE(n_fp8 == 0 || w_fp8_scales != nullptr, RDQ_E_INVALID, "w_fp8_scales must not be null when n_fp8 > 0");
+  GemvTiledArgs a;
+  a.x = static_cast<const __half *>(x);
+  a.M = M;
+  a.tiled = static_cast<const uint8_t *>(w_tiled);
+  a.s8 = w_fp8_scales;
+  a.global4 = w_fp4_global_scale;
+  a.perm = perm;
+  a.bias = static_cast<const __half *>(bias);
+  a.y = nullptr;
+  a.n4 = n_fp4;
+  a.n8 = n_fp8;
+  a.n16 = n_fp16;
+  a.K = K;
+  a.workspace = static_cast<float *>(workspace);
+  a.flags = counters;
+  a.test_timeout = 0;
+  a.n_dst = n_dst;
+  for (int d = 0; d < n_dst; ++d) {
+    RDQ_REQUIRE(dst[d] != nullptr && peer_flags[d] != nullptr, RDQ_E_INVALID, "destination %d is null", d);
+    a.dst[d] = static_cast<__half *>(dst[d]);
+    a.peer_flag[d] = peer_flags[d];
+  }
+  a.peer_state = peer_state;
+  return launch_gemv_tiled(a, (flags & RDQ_GEMV_PDL) != 0, static_cast<cudaStream_t>(stream));
+}
+
+int rdq_peer_gather(const void *buffer, const long long *index, void *y, long long count, const int32_t *flags, int world,
+                    const int32_t *peer_state, int32_t *status, int wait_ms, int flags_pdl, void *stream) {
+  RDQ_REQUIRE(count >= 0 && world >= 1 && world <= kMaxPeers && wait_ms > 0, RDQ_E_INVALID, "bad arguments to rdq_peer_gather");
+  RDQ_REQUIRE(buffer && index && y && flags && peer_state && status, RDQ_E_INVALID, "null pointer");
+  return launch_peer_gather(static_cast<const __half *>(buffer), index, static_cast<__half *>(y), count, flags, world,
+                            peer_state, status, wait_ms, (flags_pdl & RDQ_GEMV_PDL) != 0, static_cast<cudaStream_t>(stream));
+}
+
 int rdq_gemv_tiled_noalloc(const void *x, int M, const void *w_tiled, const float *w_fp8_scales,
                            float w_fp4_global_scale, const int32_t *perm, const void *bias, void *y, int n_fp4,
                            int n_fp8, int n_fp16, int K, int flags, void *stream) {

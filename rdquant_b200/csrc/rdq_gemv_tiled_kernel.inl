@@ -81,6 +81,14 @@ struct TiledArgs {
   int nepi;    // epilogue warps in use
   int fdepth;  // slots per hand-over ring
   int test_timeout;  // self-test: CTA 0 ends with a wait that runs out
+  // Peer mode (column-parallel layers): the outputs go to n_dst destinations -- one slice of a
+  // gather buffer on every GPU of the node, this one included, written with plain stores over
+  // NVLink -- instead of y; the last epilogue warp of the grid then raises this rank's flag on
+  // every GPU.  n_dst == 0: off.
+  int n_dst;
+  __half *dst[kMaxPeers];
+  int32_t *peer_flag[kMaxPeers];  // this rank's flag word on every GPU
+  int32_t *peer_state;            // local: [0] epilogue warps done in this launch, [1] launches completed
 };
 
 constexpr int kStageUnroll = 2;  // pair-loop unrolling of the NVFP4 / FP8 stages
@@ -617,12 +625,37 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
           v += __uint_as_float(bits);
           *pw = __uint_as_float(0xffffffffu);  // slot idle again
         }
-        a.y[1ll * m * N + col] = __float2half_rn(fmaf(v, scl, bia));
+        const __half h = __float2half_rn(fmaf(v, scl, bia));
+        if (a.n_dst == 0) {
+          a.y[1ll * m * N + col] = h;
+        } else {
+          // the 16 rows of a tile are consecutive columns of the slice: the stores of the lanes
+          // of one activation row fall into one 32-byte sector per destination
+          for (int d = 0; d < a.n_dst; ++d) a.dst[d][1ll * m * N + col] = h;
+        }
       }
       __syncwarp();  // vst is rewritten for the next tile
       if (__any_sync(0xffffffffu, !ok)) {
         if (lane == 0) atomicExch(status, 3);
         return;
+      }
+    }
+    if (a.n_dst > 0) {
+      // This warp's stores to the other GPUs are complete system-wide before it counts itself
+      // done; the warp that completes the count publishes the launch number in this rank's flag
+      // word on every GPU (release: fence, then the flag stores).
+      __threadfence_system();
+      __syncwarp();
+      if (lane == 0) {
+        const int expected = static_cast<int>(gridDim.x) * nepi;
+        if (atomicAdd(a.peer_state, 1) == expected - 1) {
+          __threadfence_system();
+          const int launch = a.peer_state[1] + 1;
+          a.peer_state[1] = launch;
+          a.peer_state[0] = 0;
+          for (int d = 0; d < a.n_dst; ++d)
+            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.peer_flag[d]), "r"(launch) : "memory");
+        }
       }
     }
     if (a.test_timeout && blockIdx.x == 0 && ej == 0) {
@@ -769,6 +802,12 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
   a.bias = h.bias; a.y = h.y; a.n4 = h.n4; a.n8 = h.n8; a.n16 = h.n16; a.K = h.K;
   a.workspace = h.workspace; a.flags = h.flags;
   a.test_timeout = h.test_timeout;
+  a.n_dst = h.n_dst;
+  for (int d = 0; d < kMaxPeers; ++d) {
+    a.dst[d] = d < h.n_dst ? h.dst[d] : nullptr;
+    a.peer_flag[d] = d < h.n_dst ? h.peer_flag[d] : nullptr;
+  }
+  a.peer_state = h.peer_state;
   a.status_idx = sm_count();
   a.slot_bytes = (img_bytes(0, ck) + 127) & ~127;
   const int nt = h.M <= 8 ? 1 : 2;
@@ -984,6 +1023,69 @@ int gemv_tiled_status(float *workspace, int32_t *flags, bool reset, cudaStream_t
   }
   RDQ_REQUIRE(code == 0, RDQ_E_DEVICE, "tiled GEMV: a bounded device-side wait ran out (status %d: %s); results of that launch are invalid",
               static_cast<int>(code), tiled_status_text(code));
+  return RDQ_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Peer mode, receiving side: wait (bounded) until every rank's flag on this GPU shows the
+// launch this call belongs to, then y[i] = buffer[index[i]] (un-permute out of the gather
+// buffer).
+// ---------------------------------------------------------------------------------------
+namespace {
+constexpr int kGatherThreads = 256;
+__global__ void __launch_bounds__(kGatherThreads) peer_gather_kernel(const __half *buffer, const long long *index, __half *y,
+                                                                    long long count, const int32_t *flags, int world,
+                                                                    const int32_t *sent_state, int32_t *status, int wait_ms) {
+  __shared__ int ok;
+  // let the next layer's GEMV become resident now (it only fills its weight rings until this
+  // kernel is complete), then wait for this layer's GEMV
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  // the GEMV of this launch has completed on this GPU: its launch number is the one every
+  // rank's flag must show
+  const int launch = sent_state[1];
+  if (threadIdx.x < world) {
+    int v = 0;
+    // about wait_ms milliseconds of 0.25 us naps
+    for (long long spin = 0; spin < 4000ll * wait_ms; ++spin) {
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + threadIdx.x) : "memory");
+      if (v >= launch) break;
+      __nanosleep(250);
+    }
+    if (v < launch) {
+      ok = 0;
+      atomicExch(status, 10 + static_cast<int>(threadIdx.x));  // 10 + rank that never arrived
+    }
+  }
+  __syncthreads();
+  if (!ok) return;
+  const long long stride = 1ll * gridDim.x * blockDim.x;
+  long long i = 1ll * blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < count; i += 4 * stride) {  // four independent index -> value chains in flight
+    const long long j0 = index[i], j1 = index[i + stride], j2 = index[i + 2 * stride], j3 = index[i + 3 * stride];
+    const __half v0 = buffer[j0], v1 = buffer[j1], v2 = buffer[j2], v3 = buffer[j3];
+    y[i] = v0; y[i + stride] = v1; y[i + 2 * stride] = v2; y[i + 3 * stride] = v3;
+  }
+  for (; i < count; i += stride) y[i] = buffer[index[i]];
+}
+}  // namespace
+
+int launch_peer_gather(const __half *buffer, const long long *index, __half *y, long long count, const int32_t *flags,
+                       int world, const int32_t *sent_state, int32_t *status, int wait_ms, bool pdl, cudaStream_t stream) {
+  int blocks = static_cast<int>((count + 4 * kGatherThreads - 1) / (4 * kGatherThreads));
+  blocks = std::max(1, std::min(blocks, 2 * sm_count()));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+  cfg.blockDim = dim3(kGatherThreads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  RDQ_CUDA(cudaLaunchKernelEx(&cfg, peer_gather_kernel, buffer, index, y, count, flags, world, sent_state, status, wait_ms));
   return RDQ_OK;
 }
 

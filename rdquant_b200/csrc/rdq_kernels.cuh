@@ -11,6 +11,8 @@
 
 namespace rdq {
 
+constexpr int kMaxPeers = 8;  // GPUs of one node a peer-mode launch can write to
+
 // Arguments of the decode GEMV kernels (permuted-row tensors, see rdq_b200.h).
 struct GemvArgs {
   const __half *x;
@@ -68,6 +70,11 @@ struct GemvTiledArgs {
   float *workspace;
   int32_t *flags;
   int test_timeout = 0;  // RDQ_GEMV_TEST_TIMEOUT
+  // peer mode (see TiledArgs): destinations, this rank's flag word on every GPU, local state
+  int n_dst = 0;
+  __half *dst[kMaxPeers] = {};
+  int32_t *peer_flag[kMaxPeers] = {};
+  int32_t *peer_state = nullptr;
 };
 int tiled_chunk_k(int K);
 bool tiled_supported(int n4, int n8, int n16, int K);
@@ -81,6 +88,8 @@ int gemv_tiled_noalloc(const GemvTiledArgs &a, bool pdl, cudaStream_t stream);
 // synchronise `stream`, report (and optionally clear) the kernel's status word; null scratch
 // pointers select the library array of the no-allocation entry point
 int gemv_tiled_status(float *workspace, int32_t *flags, bool reset, cudaStream_t stream);
+int launch_peer_gather(const __half *buffer, const long long *index, __half *y, long long count, const int32_t *flags,
+                       int world, const int32_t *sent_state, int32_t *status, int wait_ms, bool pdl, cudaStream_t stream);
 
 int launch_gemm(const GemmArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 // synchronise `stream`, report (and optionally clear) the GEMM's per-device status word

@@ -12,9 +12,11 @@ lookup, the FP16 lm_head and the arg-max are PyTorch in both.  A decode step has
 shapes (the KV cache is allocated for the whole run, the current position lives in a device
 tensor), so it is captured once in a CUDA graph and replayed per token.
 
-With ``world > 1`` every linear is column-parallel (``parallel.ColumnParallelMixedLinear``):
-each rank streams its rows and one NCCL all-gather per linear rebuilds the full activation on
-every rank; the glue is computed redundantly on all ranks.
+With ``world > 1`` every linear is column-parallel: each rank streams its rows and the full
+activation is rebuilt on every rank -- by stores into every GPU's gather buffer from the GEMV's
+epilogue (``parallel.PeerGatherMixedLinear``, the default) or by one NCCL all-gather per linear
+(``parallel.ColumnParallelMixedLinear``, ``peer_gather=False``, and always for the prefill GEMM);
+the glue is computed redundantly on all ranks.
 """
 from __future__ import annotations
 
@@ -76,10 +78,17 @@ class MixedDecoder:
     """Random-init decoder; weights are generated, encoded and packed layer by layer on the GPU."""
 
     def __init__(self, cfg: DecoderConfig, device, max_seq: int, batch: int, seed: int = 0, rank: int = 0,
-                 world: int = 1, group=None, use_pdl: bool = True, fused_glue: bool = True) -> None:
+                 world: int = 1, group=None, use_pdl: bool = True, fused_glue: bool = True, peer_gather: bool = True) -> None:
         self.cfg, self.device, self.max_seq, self.batch = cfg, torch.device(device), max_seq, batch
         self.rank, self.world, self.group = rank, world, group
         self.use_pdl, self.fused_glue = use_pdl, fused_glue
+        self.arena = None
+        if world > 1 and peer_gather:
+            from rdquant_b200.parallel import PeerArena
+
+            widest = max(cfg.q_heads * cfg.head_dim + 2 * cfg.kv_heads * cfg.head_dim, 2 * cfg.ffn, cfg.hidden)
+            per_layer = 4 * ((widest // world + 256) * world * 16 * 2 + 1024)
+            self.arena = PeerArena(cfg.layers * per_layer, self.device, group)
         gen = torch.Generator(device=self.device).manual_seed(seed)
         h, dh = cfg.hidden, cfg.head_dim
         nq, nkv = cfg.q_heads * dh, cfg.kv_heads * dh
@@ -144,9 +153,12 @@ class MixedDecoder:
         k = shapes[0][0]
         data, sp = fuse_layers(parts) if len(parts) > 1 else parts[0]
         if self.world > 1:
-            from rdquant_b200.parallel import ColumnParallelMixedLinear
+            from rdquant_b200.parallel import ColumnParallelMixedLinear, PeerGatherMixedLinear
 
-            mod = ColumnParallelMixedLinear(data, sp, k, self.device, self.rank, self.world, self.group)
+            if self.arena is not None:
+                mod = PeerGatherMixedLinear(data, sp, k, self.arena)
+            else:
+                mod = ColumnParallelMixedLinear(data, sp, k, self.device, self.rank, self.world, self.group)
             self.local_linear_bytes += mod.packed_bytes()
         else:
             from rdquant_b200.inference import FusedMixedLinear

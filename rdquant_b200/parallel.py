@@ -201,3 +201,174 @@ class ColumnParallelMixedLinear(nn.Module):
             return send
         y = gather_outputs(send, self.plan, self.group, buffer=buf, index=idx)
         return y.to(x.dtype).reshape(*lead, self.N)
+
+
+# ---------------------------------------------------------------------------------------------
+# All-gather fused into the GEMV epilogue: every rank stores its output slice straight into the
+# gather buffer of every GPU of the node (plain stores to peer memory over NVLink), then raises a
+# flag there; the receiving side is one small kernel that waits for the flags (bounded) and
+# un-permutes.  No NCCL call on the decode path: 4 small collectives per block cost more than the
+# GEMVs they follow.
+# ---------------------------------------------------------------------------------------------
+
+class PeerArena:
+    """One symmetric-memory allocation shared by the layers of a model: every rank allocates the
+    same bytes, the ranks exchange handles once, and layers take equal sub-ranges of it."""
+
+    def __init__(self, nbytes: int, device, group=None) -> None:
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.device = torch.device(device)
+        self.nbytes = (int(nbytes) + 255) // 256 * 256
+        self.local = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=self.device)
+        self.local.zero_()
+        torch.cuda.synchronize(self.device)
+        self.handle = symm_mem.rendezvous(self.local, self.group)
+        self.rank, self.world = int(self.handle.rank), int(self.handle.world_size)
+        self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self._used = 0
+        dist.barrier(group=self.group)  # every rank's arena is zeroed before anyone writes into one
+
+    def alloc(self, nbytes: int) -> int:
+        """Byte offset of a fresh, 256-byte aligned range of the arena (the same on every rank)."""
+        off = self._used
+        self._used = off + (int(nbytes) + 255) // 256 * 256
+        if self._used > self.nbytes:
+            raise RuntimeError(f"peer arena of {self.nbytes} bytes is full")
+        return off
+
+    def view(self, off: int, nbytes: int, dtype: torch.dtype) -> torch.Tensor:
+        return self.local[off:off + nbytes].view(dtype)
+
+
+class PeerGatherMixedLinear(nn.Module):
+    """Column-parallel mixed-precision linear whose decode path (M <= 16) needs no collective call:
+    ``rdq_gemv_tiled_peer`` writes this rank's slice into every GPU's gather buffer and
+    ``rdq_peer_gather`` waits for all slices and restores original channel order.  Larger M
+    (prefill) goes through the tcgen05 GEMM and an NCCL all-gather like
+    :class:`ColumnParallelMixedLinear`."""
+
+    MAX_M = 16
+
+    def __init__(self, layer_data: dict, splits: dict, k: int, arena: PeerArena, wait_ms: int = 500) -> None:
+        super().__init__()
+        from rdquant_b200.fused_gemv_pack import pack_for_fused_gemv
+
+        self.arena = arena
+        rank, world = arena.rank, arena.world
+        self.rank, self.world, self.group = rank, world, arena.group
+        self.device = arena.device
+        self.plan = ColumnParallelPlan.build(splits, layer_data["inv_permutation"], world)
+        self.K, self.N = int(k), sum(self.plan.splits.values())
+        shard = self.plan.shard_layer_data(layer_data, rank)
+        self.fd = pack_for_fused_gemv(shard, self.plan.local_splits(rank), k, self.device)
+        if self.fd is None or self.fd.get("w_tiled") is None:
+            raise RuntimeError("PeerGatherMixedLinear needs the built kernels and a shape with a tiled layout")
+        bias = layer_data.get("bias")
+        self.bias_local = None
+        if bias is not None:
+            self.bias_local = self.plan.local_bias(bias, rank).to(device=self.device, dtype=torch.float16)
+        n_max = self.plan.n_max
+        self._buf_off = arena.alloc(world * self.MAX_M * n_max * 2)
+        self._flag_off = arena.alloc(4 * 32)
+        self._buf_local = arena.view(self._buf_off, world * self.MAX_M * n_max * 2, torch.float16)
+        self._flags_local = arena.view(self._flag_off, 4 * 32, torch.int32)
+        # local state words: [0] warps done, [1] launches sent, [2] unused, [3] status
+        self._state = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.wait_ms = int(wait_ms)
+        self.use_pdl = False
+        self._per_m: dict = {}
+        self._nccl_state: dict = {}
+
+    def packed_bytes(self) -> int:
+        return self.plan.packed_bytes(self.rank, self.K)
+
+    def _tables(self, m: int):
+        st = self._per_m.get(m)
+        if st is None:
+            import ctypes
+
+            n_max = self.plan.n_max
+            # this rank's slice inside GPU d's gather buffer [world, m, n_max]; its flag word there
+            dst = [p + self._buf_off + self.rank * m * n_max * 2 for p in self.arena.peer_ptrs]
+            flg = [p + self._flag_off + 4 * self.rank for p in self.arena.peer_ptrs]
+            dst_arr = (ctypes.c_void_p * self.world)(*dst)
+            flg_arr = (ctypes.c_void_p * self.world)(*flg)
+            idx = self.plan.take_index(m).reshape(-1).to(self.device)
+            st = (dst_arr, flg_arr, idx)
+            self._per_m[m] = st
+        return st
+
+    def prepare(self, m: int) -> None:
+        """Build the per-M tables now (they involve a host-to-device copy, which a CUDA-graph
+        capture does not allow)."""
+        if m <= self.MAX_M:
+            self._tables(m)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        import ctypes
+
+        from rdquant_b200 import _lib, rdquant_cuda
+
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, self.K)
+        xh = (x2 if x2.dtype == torch.float16 else x2.half()).contiguous()
+        m = xh.shape[0]
+        if m > self.MAX_M:
+            send, buf, idx = self._nccl_buffers(m)
+            rdquant_cuda.mixed_linear(xh, self.fd, self.bias_local, 0, out=send)
+            y = gather_outputs(send, self.plan, self.group, buffer=buf, index=idx)
+            return y.to(x.dtype).reshape(*lead, self.N)
+        dst_arr, flg_arr, idx = self._tables(m)
+        fd = self.fd
+        y = torch.empty(m, self.N, dtype=torch.float16, device=self.device)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        p = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())  # noqa: E731
+        lib = _lib.lib()
+        rc = lib.rdq_gemv_tiled_peer(p(xh), m, p(fd["w_tiled"]), p(fd.get("w_fp8_scales")),
+                                     float(fd.get("w_fp4_global_scale", 1.0)), p(fd.get("perm")), p(self.bias_local),
+                                     ctypes.cast(dst_arr, ctypes.c_void_p), ctypes.cast(flg_arr, ctypes.c_void_p), self.world,
+                                     ctypes.c_void_p(self._state.data_ptr()), fd["n_fp4"], fd["n_fp8"], fd["n_fp16"],
+                                     self.K, p(fd["workspace"]), p(fd["tile_counters"]),
+                                     _lib.RDQ_GEMV_PDL if self.use_pdl else 0, stream)
+        _lib.check(rc, "rdq_gemv_tiled_peer")
+        rc = lib.rdq_peer_gather(p(self._buf_local), p(idx), p(y), m * self.N, p(self._flags_local), self.world,
+                                 ctypes.c_void_p(self._state.data_ptr()), ctypes.c_void_p(self._state.data_ptr() + 12),
+                                 self.wait_ms, _lib.RDQ_GEMV_PDL if self.use_pdl else 0, stream)
+        _lib.check(rc, "rdq_peer_gather")
+        return y.to(x.dtype).reshape(*lead, self.N)
+
+    def _nccl_buffers(self, m: int):
+        st = self._nccl_state.get(m)
+        if st is None:
+            send = torch.zeros(m, self.plan.n_max, dtype=torch.float16, device=self.device)
+            buf = torch.zeros(self.world, m, self.plan.n_max, dtype=torch.float16, device=self.device)
+            st = (send, buf, self.plan.take_index(m).to(self.device))
+            self._nccl_state[m] = st
+        return st
+
+    def reset_peer_state(self) -> None:
+        """Collective: after a step in which a rank did not deliver, bring the launch counters and
+        flag words of all ranks back to zero (all queued work is waited for first)."""
+        import torch.distributed as dist
+
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        self._flags_local.zero_()
+        self._state.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+
+    def check_status(self) -> None:
+        """Wait for the queued work and raise if a rank's slice never arrived (status 10 + rank) or
+        the GEMV gave up a wait; the local status word is cleared."""
+        from rdquant_b200 import rdquant_cuda
+
+        code = int(self._state[3].item())
+        if code:
+            self._state[3] = 0
+            raise RuntimeError(f"peer gather: rank {code - 10} did not deliver its slice within {self.wait_ms} ms "
+                               "(bounded device-side wait ran out); the output of that step is invalid")
+        rdquant_cuda.check_status(self.fd)
