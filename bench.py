@@ -309,7 +309,7 @@ def prefill_section(device, units, tokens=(512, 2048, 8192), steps: int = 10) ->
 
 
 def decode_section(device, batches=(1, 8), prompt: int = 512, new_tokens: int = 256, cfg=None, rank=0, world=1,
-                   gemv_block_ms=None, peer=True) -> dict:
+                   gemv_block_ms=None, peer=True, fuse_prologue=True) -> dict:
     """Whole-model greedy decoding (BASELINE configs[3]): random-init Qwen3-4B-shaped stack, all
     linears mixed-precision, `prompt`-token prefill through the GEMM, then `new_tokens` tokens, one
     CUDA-graph replay per token.  tokens/s = batch * new_tokens / device time of the decode loop."""
@@ -325,7 +325,7 @@ def decode_section(device, batches=(1, 8), prompt: int = 512, new_tokens: int = 
                                                                if peer else "NCCL all-gather per linear")
     t_build = time.time()
     model = MixedDecoder(cfg, device, max_seq=prompt + new_tokens + 8, batch=batches[0], seed=7, rank=rank, world=world,
-                         peer_gather=peer)
+                         peer_gather=peer, fuse_prologue=fuse_prologue)
     torch.cuda.synchronize()
     t_build = time.time() - t_build
     for b in batches:
@@ -578,6 +578,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel", default="tiled", choices=["tiled", "generic"])
     ap.add_argument("--no-fuse", action="store_true", help="seven launches per step instead of four")
+    ap.add_argument("--prologue", choices=["all", "norm", "act", "none"], default="all",
+                    help="whole-model decode: which of add+RMSNorm / SiLU x mul run inside the consuming GEMV")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM section")
     ap.add_argument("--no-decode", dest="decode", action="store_false", help="skip whole-model decoding")
     ap.add_argument("--decode-batches", default="1,8", help="batch sizes of the whole-model decode section")
@@ -758,7 +760,7 @@ def main() -> None:
     torch.cuda.empty_cache()
     if args.decode and m == 1:
         batches = tuple(int(b) for b in args.decode_batches.split(",") if b)
-        line["decode"] = decode_section(device, batches=batches, gemv_block_ms=ms / steps)
+        line["decode"] = decode_section(device, batches=batches, gemv_block_ms=ms / steps, fuse_prologue={"all": True, "none": False}.get(args.prologue, args.prologue))
         line["config"]["decode_tokens_per_s"] = line["decode"]["batch"][str(batches[0])]["tokens_per_s"]
     if not args.no_cpu_baseline:
         base = cpu_baseline()

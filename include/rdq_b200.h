@@ -203,6 +203,36 @@ int rdq_peer_gather(const void *buffer, const long long *index, void *y,
                     int flags_pdl, void *stream);
 
 /*
+ * rdq_gemv_tiled with an activation prologue: the kernel computes its
+ * activation rows from what the preceding kernels of a decode step left in
+ * global memory, instead of a separate kernel writing them first.  These are
+ * the element-wise steps the reference's model code runs in PyTorch between
+ * two quantized linears of a decoder block (quantized_model.py:108-190 replaces
+ * only the nn.Linear modules; the norms and the MLP activation stay with the
+ * host model).
+ *   RDQ_XOP_ADD_RMSNORM  r = x (+ x_aux, f16 add, when x_aux is not NULL);
+ *                        rows = f16(r * rsqrt(mean(r^2) + eps)) * x_weight[K];
+ *                        r is written to x_out [M, K] when x_out is not NULL
+ *                        (the updated residual stream; must not alias x or
+ *                        x_aux, which every CTA reads)
+ *   RDQ_XOP_SILU_MUL     x is [M, 2 K]; rows = f16(silu(x[:, :K])) * x[:, K:]
+ * Supported while the launcher keeps the activation rows in shared memory:
+ * rdq_gemv_tiled_stages_x(M, K) == 1 (M * (2 K + 16) bytes next to a ring of
+ * at least three weight images; K = 9728 up to M = 2, K = 2560 up to M = 8);
+ * otherwise RDQ_E_UNSUPPORTED and the caller runs rdq_add_rmsnorm /
+ * rdq_silu_mul followed by rdq_gemv_tiled.  Everything else as rdq_gemv_tiled.
+ */
+#define RDQ_XOP_ADD_RMSNORM 1
+#define RDQ_XOP_SILU_MUL 2
+int rdq_gemv_tiled_stages_x(int M, int K);
+int rdq_gemv_tiled_xop(int op, const void *x, const void *x_aux, const void *x_weight, void *x_out, float eps,
+                       int M,
+                       const void *w_tiled, const float *w_fp8_scales, float w_fp4_global_scale,
+                       const int32_t *perm, const void *bias, void *y,
+                       int n_fp4, int n_fp8, int n_fp16, int K,
+                       void *workspace, int32_t *counters, int flags, void *stream);
+
+/*
  * rdq_gemv_tiled for callers that cannot allocate device memory.  (No
  * counterpart in the reference.)  Some hosts of this library run where
  * cudaMalloc is off limits: serving loops that forbid allocation once they
@@ -335,6 +365,18 @@ int rdq_quantize_fp8(const void *w, int w_is_f32, int n, int K,
  *                       rows 0 .. *pos, grouped-query (nq % nkv == 0), positions
  *                       split over CTAs and merged by a second small kernel;
  *                       scratch: rdq_attn_decode_scratch_size bytes (f32)
+ *   rdq_rope_attn_decode  rdq_qk_rope_cache + rdq_attn_decode in ONE launch
+ *                       (head_dim 64, 128 or 256, at most 16 query heads per KV
+ *                       head): a CTA per (KV head, split of the rows) rotates
+ *                       its query heads into shared memory, brings its K / V
+ *                       rows in by cp.async tiles, and the last CTA of a KV head
+ *                       to finish merges the splits.  Same rounding points as
+ *                       the two separate calls (q and the new k are rounded to
+ *                       f16 before use).  scratch:
+ *                       rdq_rope_attn_decode_scratch_size bytes, 16-byte
+ *                       aligned, ZERO before the first call (it starts with the
+ *                       arrival counters, which every call leaves at zero); not
+ *                       to be shared by calls that may overlap.
  *   rdq_silu_mul        out[B,F] = silu(gate_up[B, 0:F]) * gate_up[B, F:2F]
  */
 int rdq_add_rmsnorm(void *x, const void *delta, const void *weight, void *out,
@@ -350,6 +392,14 @@ int rdq_attn_decode(const void *q, const void *k_cache, const void *v_cache,
                     const long long *pos, void *scratch, void *out, int B,
                     int n_q_heads, int n_kv_heads, int head_dim, int S,
                     float scale, int flags, void *stream);
+int rdq_rope_attn_decode_scratch_size(int B, int n_q_heads, int n_kv_heads,
+                                      int head_dim, int S, size_t *bytes);
+int rdq_rope_attn_decode(const void *qkv, const void *q_norm, const void *k_norm,
+                         const void *cos_table, const void *sin_table,
+                         const long long *pos, void *k_cache, void *v_cache,
+                         void *scratch, void *out, int B, int n_q_heads,
+                         int n_kv_heads, int head_dim, int S, float scale,
+                         float eps, int flags, void *stream);
 int rdq_silu_mul(const void *gate_up, void *out, int B, int F, int flags,
                  void *stream);
 

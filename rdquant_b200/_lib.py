@@ -36,6 +36,7 @@ RDQ_GEMV_AUTO = 0
 RDQ_GEMV_GENERIC = 1
 RDQ_GEMV_PDL = 16
 RDQ_GEMV_TEST_TIMEOUT = 64
+
 RDQ_E_DEVICE = -4
 
 _lock = threading.Lock()
@@ -88,6 +89,11 @@ def _bind(lib: ctypes.CDLL) -> None:
     lib.rdq_gemv_repack.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
     lib.rdq_gemv_tiled.restype = i32
     lib.rdq_gemv_tiled.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp]
+    lib.rdq_gemv_tiled_stages_x.restype = i32
+    lib.rdq_gemv_tiled_stages_x.argtypes = [i32, i32]
+    lib.rdq_gemv_tiled_xop.restype = i32
+    lib.rdq_gemv_tiled_xop.argtypes = [i32, vp, vp, vp, vp, f32, i32, vp, vp, f32, vp, vp, vp, i32, i32, i32, i32, vp, vp,
+                                       i32, vp]
     lib.rdq_gemv_tiled_peer.restype = i32
     lib.rdq_gemv_tiled_peer.argtypes = [vp, i32, vp, vp, f32, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, vp, vp, i32, vp]
     lib.rdq_peer_gather.restype = i32
@@ -120,6 +126,10 @@ def _bind(lib: ctypes.CDLL) -> None:
     lib.rdq_attn_decode_scratch_size.argtypes = [i32, i32, i32, i32, ctypes.POINTER(ctypes.c_size_t)]
     lib.rdq_attn_decode.restype = i32
     lib.rdq_attn_decode.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp]
+    lib.rdq_rope_attn_decode_scratch_size.restype = i32
+    lib.rdq_rope_attn_decode_scratch_size.argtypes = [i32, i32, i32, i32, i32, ctypes.POINTER(ctypes.c_size_t)]
+    lib.rdq_rope_attn_decode.restype = i32
+    lib.rdq_rope_attn_decode.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, f32, i32, vp]
     lib.rdq_silu_mul.restype = i32
     lib.rdq_silu_mul.argtypes = [vp, vp, i32, i32, i32, vp]
     lib.rdq_stage_copy.restype = i32
@@ -137,6 +147,8 @@ EXPORTS = [
     "rdq_gemv_tiled",
     "rdq_gemv_tiled_noalloc",
     "rdq_gemv_tiled_peer",
+    "rdq_gemv_tiled_xop",
+    "rdq_gemv_tiled_stages_x",
     "rdq_peer_gather",
     "rdq_gemv_tiled_status",
     "rdq_gemv_tiled_noalloc_status",
@@ -152,6 +164,8 @@ EXPORTS = [
     "rdq_qk_rope_cache",
     "rdq_attn_decode_scratch_size",
     "rdq_attn_decode",
+    "rdq_rope_attn_decode_scratch_size",
+    "rdq_rope_attn_decode",
     "rdq_silu_mul",
 ]
 

@@ -168,6 +168,51 @@ int rdq_gemv_tiled(const void *x, int M, const void *w_tiled, const float *w_fp8
   return launch_gemv_tiled(a, (flags & RDQ_GEMV_PDL) != 0, static_cast<cudaStream_t>(stream));
 }
 
+int rdq_gemv_tiled_stages_x(int M, int K) { return (K > 0 && K % 128 == 0 && tiled_stages_x(M, K)) ? 1 : 0; }
+int rdq_gemv_tiled_xop(int op, const void *x, const void *x_aux, const void *x_weight, void *x_out, float eps, int M,
+                       const void *w_tiled, const float *w_fp8_scales, float w_fp4_global_scale, const int32_t *perm,
+                       const void *bias, void *y, int n_fp4, int n_fp8, int n_fp16, int K, void *workspace,
+                       int32_t *counters, int flags, void *stream) {
+  RDQ_REQUIRE(op == RDQ_XOP_ADD_RMSNORM || op == RDQ_XOP_SILU_MUL, RDQ_E_INVALID, "unknown activation prologue %d", op);
+  RDQ_REQUIRE(n_fp4 >= 0 && n_fp8 >= 0 && n_fp16 >= 0 && K > 0, RDQ_E_INVALID, "bad layer shape");
+  RDQ_REQUIRE(M >= 1 && M <= RDQ_MAX_GEMV_M, RDQ_E_UNSUPPORTED, "rdq_gemv_tiled_xop takes 1..%d activation rows, got M=%d",
+              RDQ_MAX_GEMV_M, M);
+  if (n_fp4 + n_fp8 + n_fp16 == 0) return RDQ_OK;
+  RDQ_REQUIRE(tiled_supported(n_fp4, n_fp8, n_fp16, K), RDQ_E_UNSUPPORTED,
+              "shape has no tiled layout (K=%d, n=%d/%d/%d)", K, n_fp4, n_fp8, n_fp16);
+  RDQ_REQUIRE(x && y && w_tiled && workspace && counters, RDQ_E_INVALID,
+              "x, y, w_tiled, workspace and counters must not be null");
+  RDQ_REQUIRE(aligned16(x) && aligned16(w_tiled) && aligned16(x_aux) && aligned16(x_weight) && aligned16(x_out),
+              RDQ_E_INVALID, "x, x_aux, x_weight, x_out and w_tiled must be 16-byte aligned");
+  RDQ_REQUIRE(op != RDQ_XOP_ADD_RMSNORM || x_weight != nullptr, RDQ_E_INVALID, "x_weight must not be null");
+  RDQ_REQUIRE(x_out == nullptr || (x_out != x && x_out != x_aux), RDQ_E_INVALID,
+              "x_out must not alias x or x_aux: every CTA reads them");
+  RDQ_REQUIRE(n_fp8 == 0 || w_fp8_scales != nullptr, RDQ_E_INVALID, "w_fp8_scales must not be null when n_fp8 > 0");
+  GemvTiledArgs a;
+  a.x = static_cast<const __half *>(x);
+  a.M = M;
+  a.tiled = static_cast<const uint8_t *>(w_tiled);
+  a.s8 = w_fp8_scales;
+  a.global4 = w_fp4_global_scale;
+  a.perm = perm;
+  a.bias = static_cast<const __half *>(bias);
+  a.y = static_cast<__half *>(y);
+  a.n4 = n_fp4;
+  a.n8 = n_fp8;
+  a.n16 = n_fp16;
+  a.K = K;
+  a.workspace = static_cast<float *>(workspace);
+  a.flags = counters;
+  a.test_timeout = 0;
+  a.xop = op;
+  if (op == RDQ_XOP_ADD_RMSNORM) {
+    a.x_aux = static_cast<const __half *>(x_aux);
+    a.x_weight = static_cast<const __half *>(x_weight);
+    a.x_out = static_cast<__half *>(x_out);
+    a.x_eps = eps;
+  }
+  return launch_gemv_tiled(a, (flags & RDQ_GEMV_PDL) != 0, static_cast<cudaStream_t>(stream));
+}
 int rdq_gemv_tiled_peer(const void *x, int M, const void *w_tiled, const float *w_fp8_scales, float w_fp4_global_scale,
                         const int32_t *perm, const void *bias, void *const *dst, int32_t *const *peer_flags, int n_dst,
                         int32_t *peer_state, int n_fp4, int n_fp8, int n_fp16, int K, void *workspace, int32_t *counters,
@@ -378,6 +423,32 @@ int rdq_attn_decode(const void *q, const void *k_cache, const void *v_cache, con
                             static_cast<const __half *>(v_cache), pos, static_cast<float *>(scratch), static_cast<__half *>(out),
                             B, n_q_heads, n_kv_heads, head_dim, S, scale, (flags & RDQ_GEMV_PDL) != 0,
                             static_cast<cudaStream_t>(stream));
+}
+
+int rdq_rope_attn_decode_scratch_size(int B, int n_q_heads, int n_kv_heads, int head_dim, int S, size_t *bytes) {
+  RDQ_REQUIRE(bytes && B >= 0 && n_q_heads > 0 && n_kv_heads > 0 && head_dim > 0 && S > 0, RDQ_E_INVALID, "bad arguments");
+  *bytes = rope_attn_scratch_bytes(std::max(B, 1), n_q_heads, n_kv_heads, head_dim, S);
+  return RDQ_OK;
+}
+
+int rdq_rope_attn_decode(const void *qkv, const void *q_norm, const void *k_norm, const void *cos_table, const void *sin_table,
+                         const long long *pos, void *k_cache, void *v_cache, void *scratch, void *out, int B, int n_q_heads,
+                         int n_kv_heads, int head_dim, int S, float scale, float eps, int flags, void *stream) {
+  RDQ_REQUIRE(B >= 0 && n_q_heads > 0 && n_kv_heads > 0 && n_q_heads % n_kv_heads == 0 && S > 0, RDQ_E_INVALID,
+              "bad attention geometry");
+  RDQ_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, RDQ_E_UNSUPPORTED,
+              "head_dim must be 64, 128 or 256, got %d", head_dim);
+  RDQ_REQUIRE(n_q_heads / n_kv_heads <= 16, RDQ_E_UNSUPPORTED, "at most 16 query heads per KV head, got %d",
+              n_q_heads / n_kv_heads);
+  if (B == 0) return RDQ_OK;
+  RDQ_REQUIRE(qkv && cos_table && sin_table && pos && k_cache && v_cache && scratch && out, RDQ_E_INVALID, "null pointer");
+  RDQ_REQUIRE(aligned16(k_cache) && aligned16(v_cache) && aligned16(scratch), RDQ_E_INVALID,
+              "caches and scratch must be 16-byte aligned");
+  return launch_rope_attn(static_cast<const __half *>(qkv), static_cast<const __half *>(q_norm),
+                          static_cast<const __half *>(k_norm), static_cast<const __half *>(cos_table),
+                          static_cast<const __half *>(sin_table), pos, static_cast<__half *>(k_cache),
+                          static_cast<__half *>(v_cache), scratch, static_cast<__half *>(out), B, n_q_heads, n_kv_heads, head_dim,
+                          S, scale, eps, (flags & RDQ_GEMV_PDL) != 0, static_cast<cudaStream_t>(stream));
 }
 
 int rdq_silu_mul(const void *gate_up, void *out, int B, int F, int flags, void *stream) {

@@ -63,6 +63,12 @@ __device__ __forceinline__ uint32_t t_ldx4(const __half *p) {
   return v;
 }
 
+__device__ __forceinline__ uint4 ldg_cg16(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
 struct TiledArgs {
   const __half *x;
   int M;
@@ -89,6 +95,14 @@ struct TiledArgs {
   __half *dst[kMaxPeers];
   int32_t *peer_flag[kMaxPeers];  // this rank's flag word on every GPU
   int32_t *peer_state;            // local: [0] epilogue warps done in this launch, [1] launches completed
+  // Activation prologue (0: x is used as it is).  1: x_in = x (+ x_aux); the CTA's activation rows
+  // are f16(x_in * rsqrt(mean(x_in^2) + eps)) * x_weight, and CTA 0 writes x_in to x_out (the
+  // updated residual stream).  2: x is [M, 2 K] and the rows are silu(x[:, :K]) * x[:, K:].
+  int xop;
+  const __half *x_aux;
+  const __half *x_weight;
+  __half *x_out;
+  float x_eps;
 };
 
 constexpr int kStageUnroll = 2;  // pair-loop unrolling of the NVFP4 / FP8 stages
@@ -264,6 +278,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
   __shared__ __align__(8) uint64_t fl_empty[kGroups][kEpiWarps][kFlushRing];
   __shared__ __align__(8) uint64_t bar_x;
   __shared__ __align__(8) uint64_t bar_never;  // nothing ever arrives here (time-out self-test)
+  __shared__ float xred[RDQ_MAX_GEMV_M][kMmaWarps];  // activation prologue: per-warp sums of squares
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -372,10 +387,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
       // sleeps on bar_x, which completes after it (and after the activation copies).
       pdl_wait();
       const uint32_t bx = smem_u32(&bar_x);
-      if (XS) {
+      if (XS && a.xop == 0) {
         mbar_arrive_expect_tx(bx, static_cast<uint32_t>(M) * 2u * K);
         for (int m = 0; m < M; ++m) bulk_g2s(smem_u32(xsm) + m * xpitch, a.x + 1ll * m * K, 2u * K, bx);
-      } else {
+      } else {  // the MMA warps fetch (and transform) the activations themselves
         mbar_arrive(bx);
       }
     };
@@ -694,6 +709,108 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
     if (lane == 0) atomicExch(status, 6);
     return;
   }
+  if (XS && a.xop != 0) {
+    // ---- activation prologue: the twelve MMA warps build the CTA's activation rows in shared
+    // memory from what the preceding kernels left in global memory (every CTA does the same work:
+    // a few KB out of L2).  A row is cut into `cpr` chunks, one warp per chunk, and a lane has
+    // four vectors (eight with x_aux) in flight: the cost is a few L2 round trips.
+    const int nvec = K >> 3;  // 16-byte vectors per row
+    const int cpr = M >= kMmaWarps ? 1 : kMmaWarps / M;
+    const int per = (nvec + cpr - 1) / cpr;
+    if (a.xop == 1) {
+      for (int u = warp; u < M * cpr; u += kMmaWarps) {
+        const int m = u / cpr, c = u - m * cpr;
+        const int hi = min(nvec, (c + 1) * per);
+        const __half *xr = a.x + 1ll * m * K;
+        const __half *dr = a.x_aux ? a.x_aux + 1ll * m * K : nullptr;
+        __half *orow = (a.x_out && blockIdx.x == 0) ? a.x_out + 1ll * m * K : nullptr;
+        float ss = 0.f;
+        for (int i0 = c * per + lane; i0 < hi; i0 += 128) {
+          uint4 v[4], d[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            if (i0 + 32 * q < hi) v[q] = ldg_cg16(xr + 8 * (i0 + 32 * q));
+          if (dr) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              if (i0 + 32 * q < hi) d[q] = ldg_cg16(dr + 8 * (i0 + 32 * q));
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int i = i0 + 32 * q;
+            if (i >= hi) break;
+            __half2 *hv = reinterpret_cast<__half2 *>(&v[q]);
+            if (dr) {
+              const __half2 *dh = reinterpret_cast<const __half2 *>(&d[q]);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) hv[j] = __hadd2(hv[j], dh[j]);
+            }
+            if (orow) *reinterpret_cast<uint4 *>(orow + 8 * i) = v[q];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __half22float2(hv[j]);
+              ss += f.x * f.x + f.y * f.y;
+            }
+            *reinterpret_cast<uint4 *>(xsm + m * xpitch + 16 * i) = v[q];
+          }
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) xred[m][c] = ss;
+      }
+      asm volatile("bar.sync 2, %0;" ::"r"(kMmaWarps * 32) : "memory");
+      for (int u = warp; u < M * cpr; u += kMmaWarps) {
+        const int m = u / cpr, c = u - m * cpr;
+        const int hi = min(nvec, (c + 1) * per);
+        float ss = 0.f;
+        for (int w = 0; w < cpr; ++w) ss += xred[m][w];
+        const float rs = rsqrtf(ss / K + a.x_eps);
+        for (int i = c * per + lane; i < hi; i += 32) {
+          uint4 v = *reinterpret_cast<uint4 *>(xsm + m * xpitch + 16 * i);
+          const uint4 wv = *reinterpret_cast<const uint4 *>(a.x_weight + 8 * i);
+          __half2 *hv = reinterpret_cast<__half2 *>(&v);
+          const __half2 *wh = reinterpret_cast<const __half2 *>(&wv);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(hv[j]);
+            hv[j] = __hmul2(__floats2half2_rn(f.x * rs, f.y * rs), wh[j]);
+          }
+          *reinterpret_cast<uint4 *>(xsm + m * xpitch + 16 * i) = v;
+        }
+      }
+    } else {
+      for (int u = warp; u < M * cpr; u += kMmaWarps) {
+        const int m = u / cpr, c = u - m * cpr;
+        const int hi = min(nvec, (c + 1) * per);
+        const __half *gr = a.x + 2ll * m * K;
+        for (int i0 = c * per + lane; i0 < hi; i0 += 128) {
+          uint4 gv[4], uv[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            if (i0 + 32 * q < hi) {
+              gv[q] = ldg_cg16(gr + 8 * (i0 + 32 * q));
+              uv[q] = ldg_cg16(gr + K + 8 * (i0 + 32 * q));
+            }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int i = i0 + 32 * q;
+            if (i >= hi) break;
+            const __half2 *gh = reinterpret_cast<const __half2 *>(&gv[q]);
+            const __half2 *uh = reinterpret_cast<const __half2 *>(&uv[q]);
+            uint4 o;
+            __half2 *oh = reinterpret_cast<__half2 *>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 g2 = __half22float2(gh[j]);
+              const __half2 sl = __floats2half2_rn(g2.x / (1.f + __expf(-g2.x)), g2.y / (1.f + __expf(-g2.y)));
+              oh[j] = __hmul2(sl, uh[j]);
+            }
+            *reinterpret_cast<uint4 *>(xsm + m * xpitch + 16 * i) = o;
+          }
+        }
+      }
+    }
+    asm volatile("bar.sync 2, %0;" ::"r"(kMmaWarps * 32) : "memory");
+  }
   // Lanes of activation rows >= M read row 0 instead: their output columns are never stored.
   uint64_t xb[NT];
 #pragma unroll
@@ -781,6 +898,48 @@ void gemv_tiled_scratch(size_t *workspace_bytes, size_t *flag_bytes) {
   *flag_bytes = (static_cast<size_t>(G) + 2) * sizeof(int32_t);     // status word at index G
 }
 
+// Shared-memory plan of one launch: weight ring | flush ring | output metadata | activations (if
+// they fit).
+struct SmemPlan {
+  int nepi, fdep, nst, smem;
+  bool xs;
+};
+static SmemPlan smem_plan(int M, int K) {
+  SmemPlan p;
+  const int slot_bytes = (img_bytes(0, tiled_chunk_k(K)) + 127) & ~127;
+  // hand-over rings: (3 groups x nepi epilogue warps) x kFlushRing slots of 4 warps x 16 rows x
+  // (M rounded up to 4) partial sums; fewer epilogue warps for large M keep this at 18-24 KB
+  // up to four activation rows: 3 epilogue warps, 2-slot rings (18 KB at most); up to eight:
+  // 3 warps, 1-slot rings (18 KB); beyond: 2 warps, 1-slot rings (24 KB)
+  p.nepi = M <= 8 ? kEpiWarps : 2;
+  p.fdep = M <= 4 ? kFlushRing : 1;
+  const int mp = (M <= 3) ? M : ((M + 3) & ~3);
+  const int fl_bytes = kGroups * p.nepi * p.fdep * kWarpsPerGroup * kTileRows * mp * 4;
+  const int fixed = fl_bytes + kMetaSegs * kTileRows * 12 + kMaxList * 8 + kEpiWarps * kTileRows * (M <= 4 ? 4 : 16) * 4;
+  const int total_budget = 112 * 1024;  // two CTAs (this layer's and the next one's) share an SM's 228 KB
+  int xbytes = M * (2 * K + 16);
+  p.xs = true;
+  // Ring depth: slot s belongs to warp group s % 3, so depths 3k and 3k + 2 split the slots
+  // 1:1:1 and (k+1):(k+1):k; 3k + 1 would leave one group with half as many more slots as the
+  // others and measured slower than 3k.
+  auto depth = [&](int xb) {
+    int n = (total_budget - fixed - xb) / slot_bytes;
+    if (n > kMaxStages) n = kMaxStages;
+    return (n % kGroups == 1 && n > kGroups) ? n - 1 : n;
+  };
+  // activations go to shared memory while that leaves every warp group a ring slot: reading
+  // them through L1 costs more than a shallower ring (measured for M = 3 .. 8)
+  if (xbytes > 44 * 1024 || depth(xbytes) < min(kGroups, depth(0))) {
+    p.xs = false;
+    xbytes = 0;
+  }
+  p.nst = depth(xbytes);
+  if (p.nst < kGroups) p.nst = kGroups;  // 3 x 19 KB always fits beside the fixed part
+  p.smem = p.nst * slot_bytes + fixed + xbytes;
+  return p;
+}
+bool tiled_stages_x(int M, int K) { return M >= 1 && M <= RDQ_MAX_GEMV_M && smem_plan(M, K).xs; }
+
 int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
   const int ck = tiled_chunk_k(h.K);
   TSched sc;
@@ -808,42 +967,20 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
     a.peer_flag[d] = d < h.n_dst ? h.peer_flag[d] : nullptr;
   }
   a.peer_state = h.peer_state;
+  a.xop = h.xop; a.x_aux = h.x_aux; a.x_weight = h.x_weight; a.x_out = h.x_out; a.x_eps = h.x_eps;
   a.status_idx = sm_count();
   a.slot_bytes = (img_bytes(0, ck) + 127) & ~127;
   const int nt = h.M <= 8 ? 1 : 2;
-  // shared memory: weight ring | flush ring | output metadata | activations (if they fit)
-  // hand-over rings: (3 groups x nepi epilogue warps) x kFlushRing slots of 4 warps x 16 rows x
-  // (M rounded up to 4) partial sums; fewer epilogue warps for large M keep this at 18-24 KB
-  // up to four activation rows: 3 epilogue warps, 2-slot rings (18 KB at most); up to eight:
-  // 3 warps, 1-slot rings (18 KB); beyond: 2 warps, 1-slot rings (24 KB)
-  const int nepi = h.M <= 8 ? kEpiWarps : 2;
-  const int fdep = h.M <= 4 ? kFlushRing : 1;
-  a.nepi = nepi;
-  a.fdepth = fdep;
-  const int mp = (h.M <= 3) ? h.M : ((h.M + 3) & ~3);
-  const int fl_bytes = kGroups * nepi * fdep * kWarpsPerGroup * kTileRows * mp * 4;
-  const int fixed = fl_bytes + kMetaSegs * kTileRows * 12 + kMaxList * 8 + kEpiWarps * kTileRows * (h.M <= 4 ? 4 : 16) * 4;
-  const int total_budget = 112 * 1024;  // two CTAs (this layer's and the next one's) share an SM's 228 KB
-  int xbytes = h.M * (2 * h.K + 16);
-  bool xs = true;
-  // Ring depth: slot s belongs to warp group s % 3, so depths 3k and 3k + 2 split the slots
-  // 1:1:1 and (k+1):(k+1):k; 3k + 1 would leave one group with half as many more slots as the
-  // others and measured slower than 3k.
-  auto depth = [&](int xb) {
-    int n = (total_budget - fixed - xb) / a.slot_bytes;
-    if (n > kMaxStages) n = kMaxStages;
-    return (n % kGroups == 1 && n > kGroups) ? n - 1 : n;
-  };
-  // activations go to shared memory while that leaves every warp group a ring slot: reading
-  // them through L1 costs more than a shallower ring (measured for M = 3 .. 8)
-  if (xbytes > 44 * 1024 || depth(xbytes) < min(kGroups, depth(0))) {
-    xs = false;
-    xbytes = 0;
-  }
-  int nst = depth(xbytes);
-  if (nst < kGroups) nst = kGroups;  // 3 x 19 KB always fits beside the fixed part
-  a.nstages = nst;
-  const int smem = nst * a.slot_bytes + fixed + xbytes;
+  const SmemPlan pl = smem_plan(h.M, h.K);
+  a.nepi = pl.nepi;
+  a.fdepth = pl.fdep;
+  a.nstages = pl.nst;
+  const bool xs = pl.xs;
+  const int nst = pl.nst;
+  RDQ_REQUIRE(h.xop == 0 || xs, RDQ_E_UNSUPPORTED,
+              "activation prologue needs the activation rows in shared memory (M=%d, K=%d)", h.M, h.K);
+  RDQ_REQUIRE(h.xop == 0 || (h.xop == 1 && h.x_weight) || h.xop == 2, RDQ_E_INVALID, "bad activation prologue");
+  const int smem = pl.smem;
 
   // Images are balanced by what they cost a CTA in time, not by their bytes: an NVFP4 image
   // (conversion + block scaling) takes more instructions than an FP8 or FP16 image of the

@@ -222,6 +222,269 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __half *gu, __half 
   }
 }
 
+// ---- q/k RMSNorm + rotary embedding + KV-cache write + attention of the new token over the
+// cache + merge of the splits, in one launch.
+// grid = (nsplit, nkv, B), 128 threads: the CTA (split, kvh, b) serves the `group` query heads of KV
+// head kvh over the cache rows [split * chunk, (split + 1) * chunk) with chunk = the n = *pos + 1
+// rows divided by nsplit, rounded up to 32; warp w takes the heads w, w + 4, ...
+//   1. every CTA normalises and rotates its query heads into shared memory (FP16-rounded like the
+//      stored q of the separate kernel, times `scale`); the CTA whose rows include *pos does the
+//      same for the new key, copies the new value, and writes both to the cache and to its tile.
+//   2. K and V rows go to shared memory in tiles of TP rows by cp.async, two tiles in flight, so a
+//      CTA pays one memory round trip, not one per row.
+//   3. scores with one lane per row (K rows padded by 16 bytes against bank conflicts), online
+//      softmax per 32 rows, then P x V with one lane per DH / 32 dimensions.
+//   4. partial (max, sum, values) per split go to scratch; the last CTA of a (b, kvh) to arrive
+//      (counter in scratch, left at zero again) merges them and writes out [B, nq * dh].
+constexpr int kFusedAttnThreads = 128;
+constexpr int kFusedAttnMaxSplit = 32;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <int DH>
+__global__ void __launch_bounds__(kFusedAttnThreads) rope_attn_kernel(
+    const __half *qkv, const __half *qn, const __half *kn, const __half *cos_t, const __half *sin_t, const long long *pos,
+    __half *k_cache, __half *v_cache, float *part, int *counters, __half *out, int nq, int nkv, int S, float scale,
+    float eps) {
+  constexpr int TP = 8192 / DH;        // rows per tile: 16 KB of V, a little more of K
+  constexpr int KP = 2 * DH + 16;      // K row pitch in shared memory (bytes)
+  constexpr int VP = 2 * DH;
+  constexpr int HALF = DH / 2;
+  constexpr int DPL = DH / 32;         // dimensions per lane in P x V
+  constexpr int VPR = DH / 8;          // 16-byte vectors per row
+  extern __shared__ __align__(16) uint8_t smem[];
+  uint8_t *ks = smem;                           // [2][TP][KP]
+  uint8_t *vs = smem + 2 * TP * KP;             // [2][TP][VP]
+  float *qs = reinterpret_cast<float *>(vs + 2 * TP * VP);  // [group][DH]
+  __shared__ int s_last;
+
+  pdl_launch_dependents();
+  pdl_wait();
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, nsplit = gridDim.x;
+  const int group = nq / nkv;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const long long p_new = *pos;
+  const int n = static_cast<int>(p_new) + 1;
+  const int chunk = (((n + nsplit - 1) / nsplit) + 31) & ~31;
+  const int used = (n + chunk - 1) / chunk;
+  if (split >= used) return;
+  const int p0 = split * chunk, p1 = min(n, p0 + chunk);
+  const int ntile = (p1 - p0 + TP - 1) / TP;
+  const __half *kb = k_cache + (1ll * b * nkv + kvh) * S * DH;
+  const __half *vb = v_cache + (1ll * b * nkv + kvh) * S * DH;
+  const bool owns_new = p_new >= p0 && p_new < p1;
+
+  auto load_tile = [&](int t) {
+    const int r0 = p0 + t * TP, rows = min(TP, p1 - r0), st = t & 1;
+    for (int i = tid; i < rows * VPR; i += kFusedAttnThreads) {
+      const int r = i / VPR, c = i - r * VPR;
+      if (r0 + r == p_new) continue;  // the new row is not in the cache yet: step 1 puts it here
+      cp_async16(smem_u32(ks + (st * TP + r) * KP + 16 * c), kb + 1ll * (r0 + r) * DH + 8 * c);
+      cp_async16(smem_u32(vs + (st * TP + r) * VP + 16 * c), vb + 1ll * (r0 + r) * DH + 8 * c);
+    }
+    cp_async_commit();
+  };
+  load_tile(0);
+  if (ntile > 1) load_tile(1);
+
+  // ---- 1. query heads, new key and value
+  const __half *row = qkv + 1ll * b * (nq + 2 * nkv) * DH;
+  const __half *cs = cos_t + p_new * DH, *sn = sin_t + p_new * DH;
+  auto norm_rope = [&](const __half *src, const __half *nw, float (&o0)[HALF / 32], float (&o1)[HALF / 32]) {
+    float x0[HALF / 32], x1[HALF / 32], ss = 0.f;
+#pragma unroll
+    for (int t = 0; t < HALF / 32; ++t) {
+      x0[t] = __half2float(src[lane + 32 * t]);
+      x1[t] = __half2float(src[lane + 32 * t + HALF]);
+      ss += x0[t] * x0[t] + x1[t] * x1[t];
+    }
+    float rs = 1.f;
+    if (nw) rs = rsqrtf(warp_sum(ss) / DH + eps);
+#pragma unroll
+    for (int t = 0; t < HALF / 32; ++t) {
+      const int i = lane + 32 * t;
+      float y0 = x0[t], y1 = x1[t];
+      if (nw) {
+        y0 = __half2float(__hmul(__float2half_rn(x0[t] * rs), nw[i]));
+        y1 = __half2float(__hmul(__float2half_rn(x1[t] * rs), nw[i + HALF]));
+      }
+      const float c0 = __half2float(cs[i]), s0 = __half2float(sn[i]);
+      const float c1 = __half2float(cs[i + HALF]), s1 = __half2float(sn[i + HALF]);
+      o0[t] = __half2float(__float2half_rn(y0 * c0 - y1 * s0));
+      o1[t] = __half2float(__float2half_rn(y1 * c1 + y0 * s1));
+    }
+  };
+  for (int hq = warp; hq < group; hq += 4) {
+    float o0[HALF / 32], o1[HALF / 32];
+    norm_rope(row + 1ll * (kvh * group + hq) * DH, qn, o0, o1);
+#pragma unroll
+    for (int t = 0; t < HALF / 32; ++t) {
+      qs[hq * DH + lane + 32 * t] = o0[t] * scale;
+      qs[hq * DH + lane + 32 * t + HALF] = o1[t] * scale;
+    }
+  }
+  // The new row is the last row of the last tile of its CTA.  Warp 3 (key) and warp 2 (value)
+  // keep it in registers, write it to the cache now and into the tile when that tile is current.
+  float knew0[HALF / 32], knew1[HALF / 32];
+  __half vnew[DPL];
+  if (owns_new && warp == 3) {
+    norm_rope(row + 1ll * (nq + kvh) * DH, kn, knew0, knew1);
+    __half *kd = k_cache + ((1ll * b * nkv + kvh) * S + p_new) * DH;
+#pragma unroll
+    for (int t = 0; t < HALF / 32; ++t) {
+      kd[lane + 32 * t] = __float2half_rn(knew0[t]);
+      kd[lane + 32 * t + HALF] = __float2half_rn(knew1[t]);
+    }
+  }
+  if (owns_new && warp == 2) {
+    const __half *src = row + 1ll * (nq + nkv + kvh) * DH;
+    __half *vd = v_cache + ((1ll * b * nkv + kvh) * S + p_new) * DH;
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) {
+      vnew[j] = src[lane + 32 * j];
+      vd[lane + 32 * j] = vnew[j];
+    }
+  }
+
+  // ---- 2./3. tiles
+  float m_run[4], l_run[4], acc[4][DPL];  // up to 4 heads per warp (group <= 16)
+#pragma unroll
+  for (int h = 0; h < 4; ++h) {
+    m_run[h] = -INFINITY;
+    l_run[h] = 0.f;
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) acc[h][j] = 0.f;
+  }
+  for (int t = 0; t < ntile; ++t) {
+    if (t + 1 < ntile) cp_async_wait<1>(); else cp_async_wait<0>();
+    const int r0 = p0 + t * TP, rows = min(TP, p1 - r0), st = t & 1;
+    if (owns_new && t == ntile - 1) {
+      const int rr = static_cast<int>(p_new) - r0;
+      if (warp == 3) {
+        __half *sd = reinterpret_cast<__half *>(ks + (st * TP + rr) * KP);
+#pragma unroll
+        for (int u = 0; u < HALF / 32; ++u) {
+          sd[lane + 32 * u] = __float2half_rn(knew0[u]);
+          sd[lane + 32 * u + HALF] = __float2half_rn(knew1[u]);
+        }
+      }
+      if (warp == 2) {
+        __half *sd = reinterpret_cast<__half *>(vs + (st * TP + rr) * VP);
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) sd[lane + 32 * j] = vnew[j];
+      }
+    }
+    __syncthreads();  // tile t (and, the first time, qs; the last time, the new row) visible to all warps
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      const int hq = warp + 4 * h;
+      if (hq >= group) break;
+      const float4 *q4 = reinterpret_cast<const float4 *>(qs + hq * DH);
+      for (int rb = 0; rb < rows; rb += 32) {
+        const int r = rb + lane;
+        float s = -INFINITY;
+        if (r < rows) {
+          const uint4 *kr = reinterpret_cast<const uint4 *>(ks + (st * TP + r) * KP);
+          float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+          for (int c = 0; c < VPR; ++c) {
+            const uint4 kv = kr[c];
+            const float4 qa = q4[2 * c], qb = q4[2 * c + 1];
+            const float2 k0 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.x));
+            const float2 k1 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.y));
+            const float2 k2 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.z));
+            const float2 k3 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.w));
+            d0 += qa.x * k0.x + qa.y * k0.y + qa.z * k1.x + qa.w * k1.y;
+            d1 += qb.x * k2.x + qb.y * k2.y + qb.z * k3.x + qb.w * k3.y;
+          }
+          s = d0 + d1;
+        }
+        const float mn = fmaxf(m_run[h], warp_max(s));
+        const float corr = __expf(m_run[h] - mn);  // 0 the first time (m_run = -inf, mn finite)
+        const float w = (r < rows) ? __expf(s - mn) : 0.f;
+        l_run[h] = l_run[h] * corr + w;            // per-lane partial sum, reduced at the end
+        m_run[h] = mn;
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) acc[h][j] *= corr;
+        const int cnt = min(32, rows - rb);
+        const uint8_t *vrow = vs + (st * TP + rb) * VP + lane * DPL * 2;
+#pragma unroll 8
+        for (int j = 0; j < cnt; ++j) {
+          const float wj = __shfl_sync(0xffffffffu, w, j);
+          if (DPL == 4) {
+            const uint2 v = *reinterpret_cast<const uint2 *>(vrow + j * VP);
+            const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&v.x));
+            const float2 c = __half22float2(*reinterpret_cast<const __half2 *>(&v.y));
+            acc[h][0] += wj * a.x; acc[h][1] += wj * a.y; acc[h][2] += wj * c.x; acc[h][3] += wj * c.y;
+          } else {
+            const __half *vh = reinterpret_cast<const __half *>(vrow + j * VP);
+#pragma unroll
+            for (int d = 0; d < DPL; ++d) acc[h][d] += wj * __half2float(vh[d]);
+          }
+        }
+      }
+    }
+    __syncthreads();  // all warps done with stage st
+    if (t + 2 < ntile) load_tile(t + 2);
+  }
+
+  // ---- 4. partials, merge by the last CTA of this (b, kvh)
+#pragma unroll
+  for (int h = 0; h < 4; ++h) {
+    const int hq = warp + 4 * h;
+    if (hq >= group) break;
+    const float l = warp_sum(l_run[h]);
+    float *dst = part + ((1ll * b * nq + kvh * group + hq) * nsplit + split) * (DH + 2);
+    if (lane == 0) {
+      dst[0] = m_run[h];
+      dst[1] = l;
+    }
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) dst[2 + lane * DPL + j] = acc[h][j];
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(&counters[b * nkv + kvh], 1);
+    s_last = (old == used - 1);
+    if (s_last) counters[b * nkv + kvh] = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int hq = warp; hq < group; hq += 4) {
+    const int head = kvh * group + hq;
+    const float *src = part + (1ll * b * nq + head) * nsplit * (DH + 2);
+    // lane s holds split s's (max, sum); nsplit <= 32
+    const float ms = lane < used ? __ldcg(src + lane * (DH + 2)) : -INFINITY;
+    const float ls = lane < used ? __ldcg(src + lane * (DH + 2) + 1) : 0.f;
+    const float m = warp_max(ms);
+    const float w = lane < used ? __expf(ms - m) : 0.f;
+    const float l = warp_sum(ls * w);
+    float a[DPL];
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) a[j] = 0.f;
+#pragma unroll 4
+    for (int sidx = 0; sidx < used; ++sidx) {
+      const float ws = __shfl_sync(0xffffffffu, w, sidx);
+      const float *pv = src + sidx * (DH + 2) + 2 + lane * DPL;
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) a[j] += ws * __ldcg(pv + j);
+    }
+    __half *o = out + (1ll * b * nq + head) * DH + lane * DPL;
+    const float inv = 1.f / l;
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) o[j] = __float2half_rn(a[j] * inv);
+  }
+}
+
 template <typename... Args>
 int launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, bool pdl, cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t cfg = {};
@@ -263,6 +526,57 @@ int launch_attn_decode(const __half *q, const __half *k_cache, const __half *v_c
   if (rc != RDQ_OK) return rc;
   return launch_pdl(attn_combine_kernel, dim3(nq, B), dim3(dh), pdl, stream, static_cast<const float *>(scratch), out, nq, dh,
                     nsplit);
+}
+
+int rope_attn_splits(int B, int nkv, int S) {
+  int nsplit = std::min(kFusedAttnMaxSplit, std::max(1, (S + 127) / 128));
+  while (nsplit > 1 && 1ll * nsplit * nkv * B > 2ll * sm_count()) --nsplit;
+  return nsplit;
+}
+
+size_t rope_attn_scratch_bytes(int B, int nq, int nkv, int dh, int S) {
+  // counters first (4-byte ints, rounded up to 256 bytes), then the partials
+  const size_t cnt = (static_cast<size_t>(B) * nkv * sizeof(int) + 255) & ~static_cast<size_t>(255);
+  return cnt + sizeof(float) * static_cast<size_t>(B) * nq * rope_attn_splits(B, nkv, S) * (dh + 2);
+}
+
+int launch_rope_attn(const __half *qkv, const __half *qn, const __half *kn, const __half *cos_t, const __half *sin_t,
+                     const long long *pos, __half *k_cache, __half *v_cache, void *scratch, __half *out, int B, int nq,
+                     int nkv, int dh, int S, float scale, float eps, bool pdl, cudaStream_t stream) {
+  const int nsplit = rope_attn_splits(B, nkv, S);
+  const size_t cnt = (static_cast<size_t>(B) * nkv * sizeof(int) + 255) & ~static_cast<size_t>(255);
+  int *counters = static_cast<int *>(scratch);
+  float *part = reinterpret_cast<float *>(static_cast<uint8_t *>(scratch) + cnt);
+  const int group = nq / nkv;
+  const int tp = 8192 / dh;
+  const int smem = 2 * tp * (2 * dh + 16) + 2 * tp * 2 * dh + group * dh * 4;
+  static std::atomic<int> smem_set[3];  // per head_dim variant: largest dynamic shared memory asked for so far
+  auto launch = [&](auto kernel, int variant) -> int {
+    if (smem_set[variant].load() < smem) {
+      RDQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      smem_set[variant].store(smem);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(nsplit, nkv, B);
+    cfg.blockDim = dim3(kFusedAttnThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    RDQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, qkv, qn, kn, cos_t, sin_t, pos, k_cache, v_cache, part, counters, out, nq, nkv, S,
+                                scale, eps));
+    return RDQ_OK;
+  };
+  switch (dh) {
+    case 64: return launch(rope_attn_kernel<64>, 0);
+    case 128: return launch(rope_attn_kernel<128>, 1);
+    case 256: return launch(rope_attn_kernel<256>, 2);
+  }
+  RDQ_REQUIRE(false, RDQ_E_UNSUPPORTED, "head_dim must be 64, 128 or 256, got %d", dh);
+  return RDQ_OK;
 }
 
 int launch_silu_mul(const __half *gu, __half *out, int B, int F, bool pdl, cudaStream_t stream) {

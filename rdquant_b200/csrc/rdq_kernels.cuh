@@ -75,8 +75,17 @@ struct GemvTiledArgs {
   __half *dst[kMaxPeers] = {};
   int32_t *peer_flag[kMaxPeers] = {};
   int32_t *peer_state = nullptr;
+  // activation prologue (see TiledArgs)
+  int xop = 0;
+  const __half *x_aux = nullptr;
+  const __half *x_weight = nullptr;
+  __half *x_out = nullptr;
+  float x_eps = 0.f;
 };
 int tiled_chunk_k(int K);
+// true when the launcher keeps the activation rows of this shape in shared memory (a requirement
+// of the activation prologue)
+bool tiled_stages_x(int M, int K);
 bool tiled_supported(int n4, int n8, int n16, int K);
 size_t tiled_bytes(int n4, int n8, int n16, int K);
 int launch_repack(const void *w_fp4, const void *w_fp4_scales, const void *w_fp8, const void *w_fp16,
@@ -108,6 +117,12 @@ int launch_qk_rope_cache(const __half *qkv, const __half *qn, const __half *kn, 
                          const long long *pos, __half *q_out, __half *k_cache, __half *v_cache, int B, int nq, int nkv,
                          int dh, int S, float eps, bool pdl, cudaStream_t stream);
 int attn_chunk();
+// q/k norm + rotary + cache write + attention + merge of the splits in one launch
+int rope_attn_splits(int B, int nkv, int S);
+size_t rope_attn_scratch_bytes(int B, int nq, int nkv, int dh, int S);
+int launch_rope_attn(const __half *qkv, const __half *qn, const __half *kn, const __half *cos_t, const __half *sin_t,
+                     const long long *pos, __half *k_cache, __half *v_cache, void *scratch, __half *out, int B, int nq,
+                     int nkv, int dh, int S, float scale, float eps, bool pdl, cudaStream_t stream);
 int launch_attn_decode(const __half *q, const __half *k_cache, const __half *v_cache, const long long *pos, float *scratch,
                        __half *out, int B, int nq, int nkv, int dh, int S, float scale, bool pdl, cudaStream_t stream);
 int launch_silu_mul(const __half *gu, __half *out, int B, int F, bool pdl, cudaStream_t stream);

@@ -78,10 +78,12 @@ class MixedDecoder:
     """Random-init decoder; weights are generated, encoded and packed layer by layer on the GPU."""
 
     def __init__(self, cfg: DecoderConfig, device, max_seq: int, batch: int, seed: int = 0, rank: int = 0,
-                 world: int = 1, group=None, use_pdl: bool = True, fused_glue: bool = True, peer_gather: bool = True) -> None:
+                 world: int = 1, group=None, use_pdl: bool = True, fused_glue: bool = True, peer_gather: bool = True,
+                 fuse_prologue=True, fused_attention: bool = True) -> None:
         self.cfg, self.device, self.max_seq, self.batch = cfg, torch.device(device), max_seq, batch
         self.rank, self.world, self.group = rank, world, group
-        self.use_pdl, self.fused_glue = use_pdl, fused_glue
+        self.use_pdl, self.fused_glue, self.fuse_prologue = use_pdl, fused_glue, fuse_prologue
+        self.fused_attention = fused_attention and cfg.head_dim in (64, 128, 256)
         self.arena = None
         if world > 1 and peer_gather:
             from rdquant_b200.parallel import PeerArena
@@ -131,10 +133,15 @@ class MixedDecoder:
 
         f16 = dict(dtype=torch.float16, device=self.device)
         self._bufs = {
-            "x": torch.zeros(batch, cfg.hidden, **f16), "h": torch.zeros(batch, cfg.hidden, **f16),
+            "x": torch.zeros(batch, cfg.hidden, **f16), "x2": torch.zeros(batch, cfg.hidden, **f16),
+            "h": torch.zeros(batch, cfg.hidden, **f16), "down": torch.zeros(batch, cfg.hidden, **f16),
+            "qkv": torch.zeros(batch, (cfg.q_heads + 2 * cfg.kv_heads) * cfg.head_dim, **f16),
+            "gu": torch.zeros(batch, 2 * cfg.ffn, **f16),
             "q": torch.zeros(batch, cfg.q_heads, cfg.head_dim, **f16),
             "att": torch.zeros(batch, cfg.q_heads * cfg.head_dim, **f16), "act": torch.zeros(batch, cfg.ffn, **f16),
             "scratch": rdquant_cuda.attn_decode_scratch(batch, cfg.q_heads, cfg.head_dim, self.max_seq, self.device),
+            "scratch2": rdquant_cuda.rope_attn_scratch(batch, cfg.q_heads, cfg.kv_heads, cfg.head_dim, self.max_seq,
+                                                       self.device),
         }
 
     # ---- construction
@@ -214,25 +221,50 @@ class MixedDecoder:
 
     def _forward_fused(self) -> torch.Tensor:
         """One decode step (one token per sequence) with the glue kernels of rdq_glue.cu between
-        the linears instead of framework operators: 9 launches per block."""
+        the linears instead of framework operators.  On one GPU the norms and the MLP activation
+        run inside the GEMV that consumes them (activation prologue) where the batch allows:
+        6 launches per block instead of 9."""
         from rdquant_b200 import _lib, rdquant_cuda as rc
 
         cfg, st = self.cfg, self._bufs
         flags = _lib.RDQ_GEMV_PDL if self.use_pdl else 0
-        x, hbuf = st["x"], st["h"]
-        torch.index_select(self.embed, 0, self.ids, out=x)
+        b = self.batch
+        fuse = self.world == 1 and bool(self.fuse_prologue) and b <= rc.MAX_GEMV_M
+        fuse_norm = fuse and self.fuse_prologue in (True, "norm") and rc.gemv_stages_x(b, cfg.hidden)
+        fuse_act = fuse and self.fuse_prologue in (True, "act") and rc.gemv_stages_x(b, cfg.ffn)
+        cur, other, hbuf = st["x"], st["x2"], st["h"]
+        torch.index_select(self.embed, 0, self.ids, out=cur)
         delta = None
         scale = cfg.head_dim ** -0.5
+
+        def norm_linear(mod, w, out):
+            # residual += delta; out = rmsnorm(residual) @ W.T
+            nonlocal cur, other
+            if fuse_norm:
+                rc.mixed_gemv_norm(cur, delta, w, cfg.eps, mod._fd(), residual_out=other, flags=flags, out=out)
+                cur, other = other, cur
+                return out
+            rc.add_rmsnorm(cur, delta, w, hbuf, cfg.eps, flags)
+            return mod(hbuf)
+
         for blk in self.blocks:
-            rc.add_rmsnorm(x, delta, blk["ln1"], hbuf, cfg.eps, flags)
-            qkv = blk["qkv"](hbuf)
-            rc.qk_rope_cache(qkv, blk["qn"] if cfg.qk_norm else None, blk["kn"] if cfg.qk_norm else None, self.cos, self.sin,
-                             self.pos, st["q"], blk["k"], blk["v"], cfg.eps, flags)
-            rc.attn_decode(st["q"], blk["k"], blk["v"], self.pos, st["scratch"], st["att"], scale, flags)
-            rc.add_rmsnorm(x, blk["o"](st["att"]), blk["ln2"], hbuf, cfg.eps, flags)
-            rc.silu_mul(blk["gate_up"](hbuf), st["act"], flags)
-            delta = blk["down"](st["act"])
-        rc.add_rmsnorm(x, delta, self.norm, hbuf, cfg.eps, flags)
+            qkv = norm_linear(blk["qkv"], blk["ln1"], st["qkv"])
+            if self.fused_attention:
+                rc.rope_attn_decode(qkv, blk["qn"] if cfg.qk_norm else None, blk["kn"] if cfg.qk_norm else None, self.cos,
+                                    self.sin, self.pos, blk["k"], blk["v"], st["scratch2"], st["att"], cfg.q_heads, scale,
+                                    cfg.eps, flags)
+            else:
+                rc.qk_rope_cache(qkv, blk["qn"] if cfg.qk_norm else None, blk["kn"] if cfg.qk_norm else None, self.cos,
+                                 self.sin, self.pos, st["q"], blk["k"], blk["v"], cfg.eps, flags)
+                rc.attn_decode(st["q"], blk["k"], blk["v"], self.pos, st["scratch"], st["att"], scale, flags)
+            delta = blk["o"](st["att"])
+            gu = norm_linear(blk["gate_up"], blk["ln2"], st["gu"])
+            if fuse_act:
+                delta = rc.mixed_gemv_silu(gu, blk["down"]._fd(), flags=flags, out=st["down"])
+            else:
+                rc.silu_mul(gu, st["act"], flags)
+                delta = blk["down"](st["act"])
+        rc.add_rmsnorm(cur, delta, self.norm, hbuf, cfg.eps, flags)
         return hbuf @ self.lm_head.T
 
     def _step(self) -> None:

@@ -222,6 +222,53 @@ def mixed_gemv(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None, f
     return y
 
 
+XOP_ADD_RMSNORM = 1
+XOP_SILU_MUL = 2
+
+
+def gemv_stages_x(m: int, k: int) -> bool:
+    """True when the tiled GEMV keeps ``m`` activation rows of length ``k`` in shared memory,
+    which the activation prologues of :func:`mixed_gemv_norm` / :func:`mixed_gemv_silu` need."""
+    return bool(_lib.lib().rdq_gemv_tiled_stages_x(int(m), int(k)))
+
+
+def _gemv_xop(op: int, x, aux, weight, x_out, eps: float, m: int, k: int, fd: dict, bias, flags: int, out):
+    if fd.get("w_tiled") is None:
+        raise RuntimeError("the activation prologue needs the tiled layout (w_tiled)")
+    n4, n8, n16 = fd["n_fp4"], fd["n_fp8"], fd["n_fp16"]
+    if k != fd["k"]:
+        raise RuntimeError(f"activation length {k} must match K={fd['k']}")
+    y = out if out is not None else torch.empty(m, n4 + n8 + n16, dtype=torch.float16, device=x.device)
+    with _on_device(x.device):
+        rc = _lib.lib().rdq_gemv_tiled_xop(
+            op, _ptr(x), _ptr(aux), _ptr(weight), _ptr(x_out), float(eps), m, _ptr(fd["w_tiled"]),
+            _ptr(fd.get("w_fp8_scales")), float(fd.get("w_fp4_global_scale", 1.0)), _ptr(fd.get("perm")), _ptr(bias),
+            _ptr(y), n4, n8, n16, k, _ptr(fd.get("workspace")), _ptr(fd.get("tile_counters")), int(flags),
+            _stream(x.device))
+    _lib.check(rc, "rdq_gemv_tiled_xop")
+    if VALIDATE:
+        check_status(fd)
+    return y
+
+
+def mixed_gemv_norm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, fd: dict,
+                    residual_out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, flags: int = 0,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``y = rmsnorm(x + delta) @ W.T`` in one launch; ``x + delta`` goes to ``residual_out``
+    (a buffer other than ``x`` and ``delta``)."""
+    _need_cuda("x", x, torch.float16)
+    m, k = x.shape
+    return _gemv_xop(XOP_ADD_RMSNORM, x, delta, weight, residual_out, eps, m, k, fd, bias, flags, out)
+
+
+def mixed_gemv_silu(gate_up: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None, flags: int = 0,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``y = (silu(gate_up[:, :K]) * gate_up[:, K:]) @ W.T`` in one launch."""
+    _need_cuda("gate_up", gate_up, torch.float16)
+    m, k2 = gate_up.shape
+    return _gemv_xop(XOP_SILU_MUL, gate_up, None, None, None, 0.0, m, k2 // 2, fd, bias, flags, out)
+
+
 _gemm_ws: dict = {}  # device -> scratch tensor of the split-k GEMM
 
 
@@ -447,6 +494,35 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, p
         rc = _lib.lib().rdq_attn_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(pos), _ptr(scratch), _ptr(out), b, nq, nkv,
                                         dh, s, float(scale), int(flags), _stream(q.device))
     _lib.check(rc, "rdq_attn_decode")
+    return out
+
+
+def rope_attn_scratch(b: int, nq: int, nkv: int, dh: int, s: int, device) -> torch.Tensor:
+    """Zeroed scratch of :func:`rope_attn_decode` (arrival counters + per-split partials)."""
+    need = ctypes.c_size_t(0)
+    _lib.check(_lib.lib().rdq_rope_attn_decode_scratch_size(b, nq, nkv, dh, s, ctypes.byref(need)),
+               "rdq_rope_attn_decode_scratch_size")
+    return torch.zeros((need.value + 3) // 4, dtype=torch.float32, device=device)
+
+
+def rope_attn_decode(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], cos: torch.Tensor,
+                     sin: torch.Tensor, pos: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, scratch: torch.Tensor,
+                     out: torch.Tensor, nq: int, scale: float, eps: float, flags: int = 0) -> torch.Tensor:
+    """:func:`qk_rope_cache` and :func:`attn_decode` as one launch: the new token's q / k are
+    normalised and rotated, k / v written to cache row ``pos``, and ``out [B, nq * dh]`` is the
+    attention of the new token over rows ``0 .. pos``."""
+    for name, t in (("qkv", qkv), ("cos", cos), ("sin", sin), ("k_cache", k_cache), ("v_cache", v_cache), ("out", out)):
+        _need_f16(name, t)
+    _need_cuda("pos", pos, torch.int64)
+    _need_cuda("scratch", scratch, torch.float32)
+    b, nkv, s, dh = k_cache.shape
+    if qkv.shape != (b, (nq + 2 * nkv) * dh) or out.shape != (b, nq * dh):
+        raise RuntimeError("rope_attn_decode: qkv must be [B, (nq + 2 nkv) * dh] and out [B, nq * dh]")
+    with _on_device(qkv.device):
+        rc = _lib.lib().rdq_rope_attn_decode(_ptr(qkv), _ptr(q_norm), _ptr(k_norm), _ptr(cos), _ptr(sin), _ptr(pos),
+                                             _ptr(k_cache), _ptr(v_cache), _ptr(scratch), _ptr(out), b, nq, nkv, dh, s,
+                                             float(scale), float(eps), int(flags), _stream(qkv.device))
+    _lib.check(rc, "rdq_rope_attn_decode")
     return out
 
 

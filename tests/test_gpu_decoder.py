@@ -62,3 +62,18 @@ def test_prefill_and_decode_paths_agree():
             step = model._forward(ids[:, t:t + 1], 1, t).float()
     err = (full - step).abs().max() / full.abs().max()
     assert float(err) < 2e-2, float(err)
+
+
+@pytest.mark.parametrize("batch", [1, 4])
+def test_prologue_fusion_matches_separate_glue_kernels(batch):
+    """Norms and SiLU x mul folded into the consuming GEMV give the logits of the step that runs
+    them as separate kernels (the mean square is summed in another order: last-bit differences)."""
+    ids = torch.randint(0, TINY.vocab, (batch, 11), generator=torch.Generator().manual_seed(7)).cuda()
+    logits = []
+    for fuse in (True, False):
+        model = MixedDecoder(TINY, "cuda", max_seq=64, batch=batch, seed=9, fuse_prologue=fuse)
+        model.prefill(ids)
+        with torch.no_grad():
+            logits.append(model._forward_fused().float())
+    err = (logits[0] - logits[1]).abs().max() / logits[1].abs().max()
+    assert float(err) < 5e-3, float(err)

@@ -150,3 +150,73 @@ def test_fused_sibling_projections(group, m):
         assert onp.rel_err(y[:, off:off + n], y_ref) < TOL, (group, m, off)
         off += n
     assert off == y.shape[1]
+
+
+@pytest.mark.parametrize("k,n,m", [(2560, 6144, 1), (2560, 6144, 8), (2560, 19456, 3), (256, 768, 2), (4096, 2560, 4)])
+@pytest.mark.parametrize("with_delta", [False, True])
+def test_prologue_add_rmsnorm(k, n, m, with_delta):
+    """rmsnorm(x + delta) computed inside the GEMV: same result as the separate glue kernel
+    followed by the plain GEMV, and the updated residual stream is written out of place."""
+    splits = fixed_splits(n)
+    layer = random_packed_layer(splits["NVFP4"], splits["FP8"], splits["FP16"], k, seed=k + n + m)
+    fd = pack_for_fused_gemv(layer, splits, k, "cuda")
+    assert fd["w_tiled"] is not None and rdquant_cuda.gemv_stages_x(m, k)
+    g = torch.Generator().manual_seed(m + k)
+    x = torch.randn(m, k, generator=g).half().cuda()
+    d = torch.randn(m, k, generator=g).half().cuda() if with_delta else None
+    w = (1 + 0.1 * torch.randn(k, generator=g)).half().cuda()
+    x0 = x.clone()
+    res = torch.full_like(x, float("nan"))
+    y = rdquant_cuda.mixed_gemv_norm(x, d, w, 1e-6, fd, residual_out=res, flags=_lib.RDQ_GEMV_PDL)
+    assert torch.equal(x, x0)
+    # separate kernels
+    h = torch.empty_like(x)
+    x_sep = x.clone()
+    rdquant_cuda.add_rmsnorm(x_sep, d, w, h, 1e-6, 0)
+    y_sep = rdquant_cuda.mixed_gemv(h, fd)
+    assert torch.equal(res, x_sep)
+    # the two differ only by the summation order of the mean square (a last-bit change of some
+    # normalised activations)
+    scale = float(y_sep.float().abs().max())
+    assert float((y.float() - y_sep.float()).abs().max()) <= 4e-3 * scale
+    # FP32 reference of the whole formula on the dequantised weights
+    xf = x_sep.float()
+    hn = ((xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6)).half() * w).cpu()
+    y_ref = onp.mixed_precision_linear(hn.numpy(), onp.torch_layer_to_np(layer), splits, k, None)
+    assert onp.rel_err(y.cpu().float().numpy(), y_ref) < TOL
+    assert int(fd["tile_counters"].abs().sum()) == 0
+    # residual_out is optional
+    y2 = rdquant_cuda.mixed_gemv_norm(x, d, w, 1e-6, fd)
+    assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("k,n,m", [(9728, 2560, 1), (9728, 2560, 2), (512, 256, 5), (2560, 2560, 8)])
+def test_prologue_silu_mul(k, n, m):
+    """silu(gate) * up computed inside the GEMV: bit-identical to the separate kernels."""
+    splits = fixed_splits(n)
+    layer = random_packed_layer(splits["NVFP4"], splits["FP8"], splits["FP16"], k, seed=k + n + m)
+    fd = pack_for_fused_gemv(layer, splits, k, "cuda")
+    assert fd["w_tiled"] is not None and rdquant_cuda.gemv_stages_x(m, k)
+    gu = torch.randn(m, 2 * k, generator=torch.Generator().manual_seed(m)).half().cuda()
+    y = rdquant_cuda.mixed_gemv_silu(gu, fd, flags=_lib.RDQ_GEMV_PDL)
+    act = torch.empty(m, k, dtype=torch.float16, device="cuda")
+    rdquant_cuda.silu_mul(gu, act, 0)
+    y_sep = rdquant_cuda.mixed_gemv(act, fd)
+    assert torch.equal(y, y_sep)
+    assert int(fd["tile_counters"].abs().sum()) == 0
+
+
+def test_prologue_refused_when_rows_do_not_fit():
+    k, n, m = 9728, 2560, 8
+    assert not rdquant_cuda.gemv_stages_x(m, k)
+    splits = fixed_splits(n)
+    layer = random_packed_layer(splits["NVFP4"], splits["FP8"], splits["FP16"], k, seed=1)
+    fd = pack_for_fused_gemv(layer, splits, k, "cuda")
+    gu = torch.zeros(m, 2 * k, dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError, match="shared memory"):
+        rdquant_cuda.mixed_gemv_silu(gu, fd)
+    x = torch.zeros(1, 2560, dtype=torch.float16, device="cuda")
+    fd2 = pack_for_fused_gemv(random_packed_layer(128, 64, 64, 2560, seed=2), {"NVFP4": 128, "FP8": 64, "FP16": 64}, 2560,
+                              "cuda")
+    with pytest.raises(RuntimeError, match="alias"):
+        rdquant_cuda.mixed_gemv_norm(x, None, x[0], 1e-6, fd2, residual_out=x)

@@ -92,3 +92,49 @@ def test_bad_shapes_raise():
         rc.add_rmsnorm(x, None, torch.ones(12, dtype=torch.float16, device="cuda"), torch.empty_like(x), 1e-6)
     with pytest.raises(RuntimeError):
         rc.silu_mul(torch.zeros(2, 30, dtype=torch.float16, device="cuda"), torch.zeros(2, 16, dtype=torch.float16, device="cuda"))
+
+
+@pytest.mark.parametrize("b,nq,nkv,dh,norm,s,pos_v", [
+    (1, 32, 8, 128, True, 776, 520),    # the measurement decoder's geometry: 7 splits, 6 used
+    (1, 32, 8, 128, True, 776, 0),      # first token: one row, one split used
+    (1, 32, 8, 128, True, 776, 775),    # last row of the cache
+    (4, 8, 2, 64, True, 96, 37),        # one split, head_dim 64
+    (2, 64, 8, 128, False, 1500, 1333),  # 8 query heads per KV head (two per warp), several tiles per split
+    (1, 4, 4, 256, True, 5000, 4100),   # head_dim 256, one query head per KV head, 32 splits, 5 tiles per split
+    (3, 6, 2, 128, False, 200, 64),     # 3 query heads per KV head; the new row opens a 32-row block
+])
+def test_rope_attn_decode_single_launch(b, nq, nkv, dh, norm, s, pos_v):
+    """The one-launch rotary + cache write + attention gives the cache rows of rdq_qk_rope_cache
+    bit for bit and the output of rdq_attn_decode (another summation order: FP32 tolerance)."""
+    g = torch.Generator().manual_seed(nq + dh + pos_v)
+    qkv = torch.randn(b, (nq + 2 * nkv) * dh, generator=g).half().cuda()
+    qn = (1 + 0.1 * torch.randn(dh, generator=g)).half().cuda() if norm else None
+    kn = (1 + 0.1 * torch.randn(dh, generator=g)).half().cuda() if norm else None
+    inv_freq = 1.0 / (1e6 ** (torch.arange(0, dh, 2).float() / dh))
+    ang = torch.arange(s).float()[:, None] * inv_freq[None, :]
+    cos, sin = torch.cat([ang.cos(), ang.cos()], -1).half().cuda(), torch.cat([ang.sin(), ang.sin()], -1).half().cuda()
+    k_cache = (torch.randn(b, nkv, s, dh, generator=g) * 0.5).half().cuda()
+    v_cache = torch.randn(b, nkv, s, dh, generator=g).half().cuda()
+    k_cache[:, :, pos_v] = float("nan")  # stale rows at the new position must not be read
+    v_cache[:, :, pos_v] = float("nan")
+    k1, v1 = k_cache.clone(), v_cache.clone()
+    pos = torch.tensor([pos_v], dtype=torch.long, device="cuda")
+    # separate kernels
+    q_out = torch.empty(b, nq, dh, dtype=torch.float16, device="cuda")
+    rc.qk_rope_cache(qkv, qn, kn, cos, sin, pos, q_out, k1, v1, 1e-6, 0)
+    ref_out = torch.empty(b, nq * dh, dtype=torch.float16, device="cuda")
+    rc.attn_decode(q_out, k1, v1, pos, rc.attn_decode_scratch(b, nq, dh, s, "cuda"), ref_out, dh ** -0.5, 0)
+    # one launch, twice on the same scratch (the arrival counters return to zero)
+    scratch = rc.rope_attn_scratch(b, nq, nkv, dh, s, "cuda")
+    out = torch.empty(b, nq * dh, dtype=torch.float16, device="cuda")
+    for _ in range(2):
+        k2, v2 = k_cache.clone(), v_cache.clone()
+        out.fill_(float("nan"))
+        rc.rope_attn_decode(qkv, qn, kn, cos, sin, pos, k2, v2, scratch, out, nq, dh ** -0.5, 1e-6, _lib.RDQ_GEMV_PDL)
+        assert torch.equal(k2, k1) and torch.equal(v2, v1)
+        _close(out, ref_out)
+    mask = (torch.arange(s, device="cuda") <= pos_v)[None, None, None, :]
+    ref = F.scaled_dot_product_attention(q_out[:, :, None, :].float(), k1.float(), v1.float(), attn_mask=mask, enable_gqa=True)
+    _close(out, ref.reshape(b, nq * dh))
+    nbytes = (b * nkv * 4 + 255) // 256 * 256
+    assert int(scratch.view(torch.int32)[: nbytes // 4].abs().sum()) == 0
