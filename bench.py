@@ -583,6 +583,8 @@ def main() -> None:
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM section")
     ap.add_argument("--no-decode", dest="decode", action="store_false", help="skip whole-model decoding")
     ap.add_argument("--decode-batches", default="1,8", help="batch sizes of the whole-model decode section")
+    ap.add_argument("--decode-prompt", type=int, default=512, help="prompt tokens of the decode section")
+    ap.add_argument("--decode-tokens", type=int, default=256, help="generated tokens of the decode section")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="N > 1: all-gather fused into the GEMV epilogue over peer memory, or NCCL")
     ap.set_defaults(decode=True)
@@ -760,7 +762,9 @@ def main() -> None:
     torch.cuda.empty_cache()
     if args.decode and m == 1:
         batches = tuple(int(b) for b in args.decode_batches.split(",") if b)
-        line["decode"] = decode_section(device, batches=batches, gemv_block_ms=ms / steps, fuse_prologue={"all": True, "none": False}.get(args.prologue, args.prologue))
+        line["decode"] = decode_section(device, batches=batches, prompt=args.decode_prompt, new_tokens=args.decode_tokens,
+                                        gemv_block_ms=ms / steps,
+                                        fuse_prologue={"all": True, "none": False}.get(args.prologue, args.prologue))
         line["config"]["decode_tokens_per_s"] = line["decode"]["batch"][str(batches[0])]["tokens_per_s"]
     if not args.no_cpu_baseline:
         base = cpu_baseline()

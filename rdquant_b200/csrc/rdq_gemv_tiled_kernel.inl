@@ -268,7 +268,9 @@ __device__ __forceinline__ void tile_geom(const TSched &sc, int gtile, int &firs
 }
 
 // NT = number of 8-row activation groups (1: M <= 8, 2: M <= 16)
-template <int NT, bool XS>
+// EXTRA: the launch has an activation prologue or peer destinations (compiled apart so that the
+// plain launch carries none of that code)
+template <int NT, bool XS, bool EXTRA>
 __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_constant__ TiledArgs a,
                                                   const __grid_constant__ TSched sc) {
   extern __shared__ __align__(128) uint8_t smem[];
@@ -278,7 +280,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
   __shared__ __align__(8) uint64_t fl_empty[kGroups][kEpiWarps][kFlushRing];
   __shared__ __align__(8) uint64_t bar_x;
   __shared__ __align__(8) uint64_t bar_never;  // nothing ever arrives here (time-out self-test)
-  __shared__ float xred[RDQ_MAX_GEMV_M][kMmaWarps];  // activation prologue: per-warp sums of squares
+  __shared__ float xred[EXTRA ? RDQ_MAX_GEMV_M : 1][kMmaWarps];  // activation prologue: per-warp sums of squares
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -387,7 +389,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
       // sleeps on bar_x, which completes after it (and after the activation copies).
       pdl_wait();
       const uint32_t bx = smem_u32(&bar_x);
-      if (XS && a.xop == 0) {
+      if (XS && (!EXTRA || a.xop == 0)) {
         mbar_arrive_expect_tx(bx, static_cast<uint32_t>(M) * 2u * K);
         for (int m = 0; m < M; ++m) bulk_g2s(smem_u32(xsm) + m * xpitch, a.x + 1ll * m * K, 2u * K, bx);
       } else {  // the MMA warps fetch (and transform) the activations themselves
@@ -641,7 +643,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
           *pw = __uint_as_float(0xffffffffu);  // slot idle again
         }
         const __half h = __float2half_rn(fmaf(v, scl, bia));
-        if (a.n_dst == 0) {
+        if (!EXTRA || a.n_dst == 0) {
           a.y[1ll * m * N + col] = h;
         } else {
           // the 16 rows of a tile are consecutive columns of the slice: the stores of the lanes
@@ -655,7 +657,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
         return;
       }
     }
-    if (a.n_dst > 0) {
+    if (EXTRA && a.n_dst > 0) {
       // This warp's stores to the other GPUs are complete system-wide before it counts itself
       // done; the warp that completes the count publishes the launch number in this rank's flag
       // word on every GPU (release: fence, then the flag stores).
@@ -709,7 +711,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tiled_kernel(const __grid_co
     if (lane == 0) atomicExch(status, 6);
     return;
   }
-  if (XS && a.xop != 0) {
+  if (EXTRA && XS && a.xop != 0) {
     // ---- activation prologue: the twelve MMA warps build the CTA's activation rows in shared
     // memory from what the preceding kernels left in global memory (every CTA does the same work:
     // a few KB out of L2).  A row is cut into `cpr` chunks, one warp per chunk, and a lane has
@@ -1033,16 +1035,23 @@ int launch_gemv_tiled(const GemvTiledArgs &h, bool pdl, cudaStream_t stream) {
   RDQ_REQUIRE(sc.W / G / sc.u16 + 2 <= kMaxList, RDQ_E_UNSUPPORTED,
               "layer too large for the tiled GEMV: more than %d images per CTA", kMaxList);
 
-  static int smem_set[64][4] = {};
+  static int smem_set[64][8] = {};
   static std::mutex smem_mutex;
   int dev = 0;
   RDQ_CUDA(cudaGetDevice(&dev));
   std::lock_guard<std::mutex> smem_lock(smem_mutex);
-  const int variant = (nt - 1) * 2 + (xs ? 1 : 0);
-  const void *fn = variant == 0 ? reinterpret_cast<const void *>(gemv_tiled_kernel<1, false>)
-                   : variant == 1 ? reinterpret_cast<const void *>(gemv_tiled_kernel<1, true>)
-                   : variant == 2 ? reinterpret_cast<const void *>(gemv_tiled_kernel<2, false>)
-                                  : reinterpret_cast<const void *>(gemv_tiled_kernel<2, true>);
+  const bool extra = h.xop != 0 || h.n_dst > 0;
+  const int variant = (extra ? 4 : 0) + (nt - 1) * 2 + (xs ? 1 : 0);
+  static const void *const fns[8] = {
+      reinterpret_cast<const void *>(gemv_tiled_kernel<1, false, false>),
+      reinterpret_cast<const void *>(gemv_tiled_kernel<1, true, false>),
+      reinterpret_cast<const void *>(gemv_tiled_kernel<2, false, false>),
+      reinterpret_cast<const void *>(gemv_tiled_kernel<2, true, false>),
+      reinterpret_cast<const void *>(gemv_tiled_kernel<1, false, true>),
+      reinterpret_cast<const void *>(gemv_tiled_kernel<1, true, true>),
+      reinterpret_cast<const void *>(gemv_tiled_kernel<2, false, true>),
+      reinterpret_cast<const void *>(gemv_tiled_kernel<2, true, true>)};
+  const void *fn = fns[variant];
   if (dev < 64 && smem_set[dev][variant] < smem) {
     RDQ_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     // Always the largest shared-memory carve-out: layers of different footprints follow each

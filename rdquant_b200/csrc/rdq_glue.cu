@@ -270,6 +270,19 @@ __global__ void __launch_bounds__(kFusedAttnThreads) rope_attn_kernel(
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, nsplit = gridDim.x;
   const int group = nq / nkv;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // Loads that do not depend on the position go first, so that they share a round trip with it:
+  // the raw values of this warp's first query head and the norm weights.
+  const __half *row = qkv + 1ll * b * (nq + 2 * nkv) * DH;
+  float qx0[HALF / 32], qx1[HALF / 32], qw0[HALF / 32], qw1[HALF / 32];
+  auto load_row = [&](const __half *src, float (&x0)[HALF / 32], float (&x1)[HALF / 32]) {
+#pragma unroll
+    for (int t = 0; t < HALF / 32; ++t) {
+      x0[t] = __half2float(src[lane + 32 * t]);
+      x1[t] = __half2float(src[lane + 32 * t + HALF]);
+    }
+  };
+  if (warp < group) load_row(row + 1ll * (kvh * group + warp) * DH, qx0, qx1);
+  if (qn) load_row(qn, qw0, qw1);
   const long long p_new = *pos;
   const int n = static_cast<int>(p_new) + 1;
   const int chunk = (((n + nsplit - 1) / nsplit) + 31) & ~31;
@@ -295,35 +308,39 @@ __global__ void __launch_bounds__(kFusedAttnThreads) rope_attn_kernel(
   if (ntile > 1) load_tile(1);
 
   // ---- 1. query heads, new key and value
-  const __half *row = qkv + 1ll * b * (nq + 2 * nkv) * DH;
   const __half *cs = cos_t + p_new * DH, *sn = sin_t + p_new * DH;
-  auto norm_rope = [&](const __half *src, const __half *nw, float (&o0)[HALF / 32], float (&o1)[HALF / 32]) {
-    float x0[HALF / 32], x1[HALF / 32], ss = 0.f;
+  float c0[HALF / 32], s0[HALF / 32], c1[HALF / 32], s1[HALF / 32];
 #pragma unroll
-    for (int t = 0; t < HALF / 32; ++t) {
-      x0[t] = __half2float(src[lane + 32 * t]);
-      x1[t] = __half2float(src[lane + 32 * t + HALF]);
-      ss += x0[t] * x0[t] + x1[t] * x1[t];
-    }
+  for (int t = 0; t < HALF / 32; ++t) {
+    const int i = lane + 32 * t;
+    c0[t] = __half2float(cs[i]);
+    s0[t] = __half2float(sn[i]);
+    c1[t] = __half2float(cs[i + HALF]);
+    s1[t] = __half2float(sn[i + HALF]);
+  }
+  // RMSNorm over the head (when nw), rotary embedding; FP16-rounded results as floats
+  auto norm_rope = [&](const float (&x0)[HALF / 32], const float (&x1)[HALF / 32], bool nw, const float (&w0)[HALF / 32],
+                       const float (&w1)[HALF / 32], float (&o0)[HALF / 32], float (&o1)[HALF / 32]) {
+    float ss = 0.f;
+#pragma unroll
+    for (int t = 0; t < HALF / 32; ++t) ss += x0[t] * x0[t] + x1[t] * x1[t];
     float rs = 1.f;
     if (nw) rs = rsqrtf(warp_sum(ss) / DH + eps);
 #pragma unroll
     for (int t = 0; t < HALF / 32; ++t) {
-      const int i = lane + 32 * t;
       float y0 = x0[t], y1 = x1[t];
       if (nw) {
-        y0 = __half2float(__hmul(__float2half_rn(x0[t] * rs), nw[i]));
-        y1 = __half2float(__hmul(__float2half_rn(x1[t] * rs), nw[i + HALF]));
+        y0 = __half2float(__hmul(__float2half_rn(x0[t] * rs), __float2half_rn(w0[t])));
+        y1 = __half2float(__hmul(__float2half_rn(x1[t] * rs), __float2half_rn(w1[t])));
       }
-      const float c0 = __half2float(cs[i]), s0 = __half2float(sn[i]);
-      const float c1 = __half2float(cs[i + HALF]), s1 = __half2float(sn[i + HALF]);
-      o0[t] = __half2float(__float2half_rn(y0 * c0 - y1 * s0));
-      o1[t] = __half2float(__float2half_rn(y1 * c1 + y0 * s1));
+      o0[t] = __half2float(__float2half_rn(y0 * c0[t] - y1 * s0[t]));
+      o1[t] = __half2float(__float2half_rn(y1 * c1[t] + y0 * s1[t]));
     }
   };
   for (int hq = warp; hq < group; hq += 4) {
     float o0[HALF / 32], o1[HALF / 32];
-    norm_rope(row + 1ll * (kvh * group + hq) * DH, qn, o0, o1);
+    if (hq != warp) load_row(row + 1ll * (kvh * group + hq) * DH, qx0, qx1);
+    norm_rope(qx0, qx1, qn != nullptr, qw0, qw1, o0, o1);
 #pragma unroll
     for (int t = 0; t < HALF / 32; ++t) {
       qs[hq * DH + lane + 32 * t] = o0[t] * scale;
@@ -335,7 +352,10 @@ __global__ void __launch_bounds__(kFusedAttnThreads) rope_attn_kernel(
   float knew0[HALF / 32], knew1[HALF / 32];
   __half vnew[DPL];
   if (owns_new && warp == 3) {
-    norm_rope(row + 1ll * (nq + kvh) * DH, kn, knew0, knew1);
+    float kx0[HALF / 32], kx1[HALF / 32], kw0[HALF / 32], kw1[HALF / 32];
+    load_row(row + 1ll * (nq + kvh) * DH, kx0, kx1);
+    if (kn) load_row(kn, kw0, kw1);
+    norm_rope(kx0, kx1, kn != nullptr, kw0, kw1, knew0, knew1);
     __half *kd = k_cache + ((1ll * b * nkv + kvh) * S + p_new) * DH;
 #pragma unroll
     for (int t = 0; t < HALF / 32; ++t) {

@@ -115,8 +115,18 @@ def pack_for_fused_gemv(layer_data: dict, splits: dict, k: int, device,
         "parallel_k": 1,
         "n_fp4": n4, "n_fp8": n8, "n_fp16": n16, "k": int(k),
     }
-    # re-tiled copy for the fast decode kernel (None when the shape has no tiled layout)
-    fd["w_tiled"] = rdquant_cuda.repack_tiled(fd) if tiled else None
+    # re-tiled copy for the fast decode kernel (None when the shape has no tiled layout): taken
+    # from the checkpoint when it carries one of the right size
+    # (integrations.hf_export.save_tiled_layout), else produced here
+    fd["w_tiled"] = None
+    if tiled:
+        stored = layer_data.get("weight_tiled")
+        need = rdquant_cuda.tiled_bytes(n4, n8, n16, int(k))
+        if stored is not None and need and stored.dtype == torch.uint8 and stored.numel() == need:
+            fd["w_tiled"] = stored.reshape(-1).to(device).contiguous()
+            fd["tiled_from_checkpoint"] = True
+        else:
+            fd["w_tiled"] = rdquant_cuda.repack_tiled(fd)
     return fd
 
 

@@ -259,6 +259,10 @@ def load_for_inference(
         for key in fh.keys():
             tensors[key] = fh.get_tensor(key)
 
+    # the decode kernel's tiling, when the checkpoint carries it (hf_export.save_tiled_layout)
+    from rdquant_b200.integrations.hf_export import read_tiled_layout
+
+    tensors.update(read_tiled_layout(checkpoint_dir))
     replace_quantized_layers(model, layer_configs, tensors, target)
 
     quant_layers = tuple(name + "." for name in layer_configs)

@@ -132,6 +132,59 @@ def save_packed(model, path: str, source_model_dir: str | None = None) -> None:
                 shutil.copy2(src, os.path.join(path, fname))
 
 
+TILED_FILE = "model.tiled.safetensors"
+TILED_LAYOUT = "rdq_b200_tiled_v1"
+
+
+def save_tiled_layout(path: str, device: str = "cuda") -> dict:
+    """Add the decode kernel's in-memory tiling to a packed checkpoint, so that loading it is a
+    plain upload with no re-tiling pass.
+
+    For every quantised layer whose shape has a tiled layout, the image stream
+    ``rdq_gemv_repack`` produces (include/rdq_b200.h) is written as ``<layer>.weight_tiled``
+    (uint8) into ``model.tiled.safetensors`` next to ``model.safetensors``; the latter is not
+    touched, so the checkpoint still round-trips through the reference's ``load_packed``
+    (rdquant/integrations/hf_export.py:199-375).  The file's metadata names the layout version;
+    :func:`rdquant_b200.inference.load_for_inference` ignores a file of another version or a
+    tensor whose size does not match ``rdq_gemv_tiled_bytes``.  Needs a CUDA device (the tiling
+    is produced by the device kernel).  Returns ``{"layers": count, "bytes": total}``.
+    """
+    from safetensors.torch import save_file
+
+    from rdquant_b200.fused_gemv_pack import pack_for_fused_gemv
+
+    config, tensors = read_layers(path)
+    out: dict[str, torch.Tensor] = {}
+    for name, lconf in config["layers"].items():
+        pre = name + "."
+        layer_data = {k[len(pre):]: v for k, v in tensors.items() if k.startswith(pre)}
+        fd = pack_for_fused_gemv(layer_data, lconf["splits"], lconf["in_features"], device)
+        if fd is None:
+            raise RuntimeError("save_tiled_layout needs the built rdquant_b200 kernels and a CUDA device")
+        if fd.get("w_tiled") is not None:
+            out[pre + "weight_tiled"] = fd["w_tiled"].cpu().contiguous()
+        del fd
+    save_file(out, os.path.join(path, TILED_FILE), metadata={"layout": TILED_LAYOUT})
+    return {"layers": len(out), "bytes": int(sum(t.numel() for t in out.values()))}
+
+
+def read_tiled_layout(path: str) -> dict:
+    """``{tensor name: uint8 tensor}`` of ``model.tiled.safetensors`` (empty when the file is
+    absent or of another layout version)."""
+    from safetensors import safe_open
+
+    fname = os.path.join(path, TILED_FILE)
+    if not os.path.isfile(fname):
+        return {}
+    out = {}
+    with safe_open(fname, framework="pt", device="cpu") as fh:
+        if (fh.metadata() or {}).get("layout") != TILED_LAYOUT:
+            return {}
+        for key in fh.keys():
+            out[key] = fh.get_tensor(key)
+    return out
+
+
 def unpack_nvfp4_codes(packed: torch.Tensor) -> torch.Tensor:
     """[n, K/2] uint8 -> [n, K] int64 codes (low nibble = even k)."""
     n, half = packed.shape

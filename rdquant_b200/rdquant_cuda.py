@@ -165,6 +165,11 @@ def dequantize_packed(layer_data: dict, splits: dict, k: int, inv_perm: Optional
     return out
 
 
+def tiled_bytes(n4: int, n8: int, n16: int, k: int) -> int:
+    """Size of the tiled copy of a layer (0: the shape has no tiled layout)."""
+    return int(_lib.lib().rdq_gemv_tiled_bytes(n4, n8, n16, k))
+
+
 def repack_tiled(fd: dict) -> Optional[torch.Tensor]:
     """Re-tile the row-major buffers of a ``pack_for_fused_gemv`` dict for the fast GEMV;
     ``None`` when the shape has no tiled layout."""
@@ -366,8 +371,8 @@ def quantize_nvfp4_packed(w: torch.Tensor, want_sqerr: bool = False) -> dict:
 
     Returns the checkpoint tensors ``weight_nvfp4`` u8 [n, K/2] and ``weight_nvfp4_scale`` u8
     [n, K/16], bit-identical to the reference encoder + writer (rdquant/core/formats.py:84-142,
-    rdquant/integrations/hf_export.py:81-92), ``global_scale`` (largest block scale, 1.0 if all
-    are zero) and, on request, ``row_sqerr`` f32 [n] = per-row sum of squared reconstruction errors.
+    rdquant/integrations/hf_export.py:81-92), ``global_scale`` (largest block scale; 0.0 for an
+    all-zero group, which ``quantize.quantize_weight_packed`` stores as 1.0 like the reference) and, on request, ``row_sqerr`` f32 [n] = per-row sum of squared reconstruction errors.
     """
     _need_cuda("w", w)
     if w.dim() != 2 or w.dtype not in (torch.float16, torch.float32):

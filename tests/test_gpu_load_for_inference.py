@@ -96,3 +96,44 @@ def test_loaded_model_matches_dense_dequantised_model(tmp_path):
             ref = dense(input_ids=ids).logits.float()
         err = (got - ref).abs().max() / ref.abs().max()
         assert float(err) < 1e-2, (tokens, float(err))
+
+
+@pytest.mark.gpu
+def test_tiled_layout_in_checkpoint_is_used_as_is(tmp_path):
+    """save_tiled_layout writes the decode kernel's tiling beside the checkpoint (which keeps its
+    bytes); a load then uploads it instead of re-tiling, and the model computes the same logits
+    bit for bit.  A file of another layout version, or a tensor of the wrong size, is ignored."""
+    import hashlib
+
+    from safetensors.torch import save_file
+
+    from rdquant_b200.inference import load_for_inference
+
+    names = write_checkpoint(str(tmp_path))
+    main = os.path.join(tmp_path, "model.safetensors")
+    sha = hashlib.sha256(open(main, "rb").read()).hexdigest()
+    plain = load_for_inference(str(tmp_path), device="cuda")
+    assert not any(plain.get_submodule(n)._fd().get("tiled_from_checkpoint") for n in names)
+
+    info = hf_export.save_tiled_layout(str(tmp_path), device="cuda")
+    assert info["layers"] == len(names) and info["bytes"] > 0
+    assert hashlib.sha256(open(main, "rb").read()).hexdigest() == sha
+    fast = load_for_inference(str(tmp_path), device="cuda")
+    for n in names:
+        a, b = plain.get_submodule(n)._fd(), fast.get_submodule(n)._fd()
+        assert b.get("tiled_from_checkpoint") and torch.equal(a["w_tiled"], b["w_tiled"]), n
+    ids = torch.randint(0, 512, (1, 5), generator=torch.Generator().manual_seed(2)).cuda()
+    with torch.no_grad():
+        assert torch.equal(plain(input_ids=ids).logits, fast(input_ids=ids).logits)
+
+    # wrong size -> re-tiled at load; other layout version -> file ignored
+    tiled = hf_export.read_tiled_layout(str(tmp_path))
+    key = names[0] + ".weight_tiled"
+    tiled[key] = tiled[key][:-16].contiguous()
+    save_file(tiled, os.path.join(tmp_path, hf_export.TILED_FILE), metadata={"layout": hf_export.TILED_LAYOUT})
+    again = load_for_inference(str(tmp_path), device="cuda")
+    assert not again.get_submodule(names[0])._fd().get("tiled_from_checkpoint")
+    assert again.get_submodule(names[1])._fd().get("tiled_from_checkpoint")
+    assert torch.equal(again.get_submodule(names[0])._fd()["w_tiled"], plain.get_submodule(names[0])._fd()["w_tiled"])
+    save_file(tiled, os.path.join(tmp_path, hf_export.TILED_FILE), metadata={"layout": "something else"})
+    assert hf_export.read_tiled_layout(str(tmp_path)) == {}
