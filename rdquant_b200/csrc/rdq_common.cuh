@@ -195,6 +195,23 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// A CTA without work stays resident for a few microseconds instead of returning at once.  The
+// decode chain relies on every SM holding exactly one CTA of each launch: the CTAs of the GEMV
+// after this kernel are placed, one per SM, into the slots the GEMV before it frees.  A CTA of
+// this kernel that returned at the same moment would free a second slot on its SM, two CTAs of
+// that GEMV would land there, run at half speed each, and the whole launch would wait for them
+// (measured: 52 of 148 SMs doubled, +60 % on the following GEMVs).  After the linger all pending
+// CTAs of that GEMV are placed and the freed slot goes to the launch after it.
+__device__ __forceinline__ void linger(unsigned int ns) {
+  unsigned long long t0, t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (int i = 0; i < 64; ++i) {  // bounded: 64 naps of at most 0.25 us
+    __nanosleep(250);
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (t - t0 > ns) break;
+  }
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

@@ -1220,12 +1220,14 @@ __global__ void __launch_bounds__(kGatherThreads) peer_gather_kernel(const __hal
 
 int launch_peer_gather(const __half *buffer, const long long *index, __half *y, long long count, const int32_t *flags,
                        int world, const int32_t *sent_state, int32_t *status, int wait_ms, bool pdl, cudaStream_t stream) {
-  int blocks = static_cast<int>((count + 4 * kGatherThreads - 1) / (4 * kGatherThreads));
-  blocks = std::max(1, std::min(blocks, 2 * sm_count()));
+  // one CTA per SM, each with the footprint that keeps a second one off its SM (pin_slot); every
+  // CTA waits for the flags, so none leaves before the GEMV after this kernel has its CTAs placed
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+  cfg.gridDim = dim3(static_cast<unsigned>(sm_count()));
   cfg.blockDim = dim3(kGatherThreads);
+  cfg.dynamicSmemBytes = kSlotSmem;
   cfg.stream = stream;
+  RDQ_CUDA(pin_slot(reinterpret_cast<const void *>(peer_gather_kernel), kSlotSmem));
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;

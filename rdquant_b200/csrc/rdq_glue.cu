@@ -12,6 +12,9 @@
 // griddepcontrol.wait.  All arithmetic is FP32 with one rounding to FP16 per stored value.
 #include "rdq_kernels.cuh"
 
+#include <utility>
+#include <vector>
+
 namespace rdq {
 
 namespace {
@@ -28,10 +31,14 @@ __device__ __forceinline__ float block_sum(float v, float *smem) {
 
 // ---- x (+= delta); out = rmsnorm(x) * w.  One CTA per row.
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(__half *x, const __half *delta, const __half *w, __half *out,
-                                                         int H, float eps) {
+                                                         int B, int H, float eps) {
   __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
+  if (static_cast<int>(blockIdx.x) >= B) {  // the grid has a CTA per SM (see linger())
+    linger(1500);
+    return;
+  }
   __half *xr = x + 1ll * blockIdx.x * H;
   const __half *dr = delta ? delta + 1ll * blockIdx.x * H : nullptr;
   float ss = 0.f;
@@ -202,8 +209,16 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const float *part, __
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __half *gu, __half *out, int B, int F) {
   pdl_launch_dependents();
   pdl_wait();
+  // every CTA takes an equal, contiguous share of the 16-byte vectors, so that (nearly) all SMs
+  // work and leave together
   const long long total = 1ll * B * (F / 8);
-  for (long long i = 1ll * blockIdx.x * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
+  const long long per = (total + gridDim.x - 1) / gridDim.x;
+  const long long lo = per * blockIdx.x, hi = lo + per < total ? lo + per : total;
+  if (lo >= total) {  // the grid has a CTA per SM (see linger())
+    linger(1500);
+    return;
+  }
+  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
     const int b = static_cast<int>(i / (F / 8)), j = static_cast<int>(i - 1ll * b * (F / 8));
     const uint4 g = reinterpret_cast<const uint4 *>(gu + 2ll * b * F)[j];
     const uint4 u = reinterpret_cast<const uint4 *>(gu + 2ll * b * F + F)[j];
@@ -224,8 +239,9 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __half *gu, __half 
 
 // ---- q/k RMSNorm + rotary embedding + KV-cache write + attention of the new token over the
 // cache + merge of the splits, in one launch.
-// grid = (nsplit, nkv, B), 128 threads: the CTA (split, kvh, b) serves the `group` query heads of KV
-// head kvh over the cache rows [split * chunk, (split + 1) * chunk) with chunk = the n = *pos + 1
+// One CTA per SM, 128 threads: CTA c is (sequence, KV head) c / nsplit and split c % nsplit, with
+// nsplit = SMs / (sequences x KV heads) (at most 32); it serves the `group` query heads of its KV
+// head over the cache rows [split * chunk, (split + 1) * chunk) with chunk = the n = *pos + 1
 // rows divided by nsplit, rounded up to 32; warp w takes the heads w, w + 4, ...
 //   1. every CTA normalises and rotates its query heads into shared memory (FP16-rounded like the
 //      stored q of the separate kernel, times `scale`); the CTA whose rows include *pos does the
@@ -236,7 +252,8 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __half *gu, __half 
 //      softmax per 32 rows, then P x V with one lane per DH / 32 dimensions.
 //   4. partial (max, sum, values) per split go to scratch; the last CTA of a (b, kvh) to arrive
 //      (counter in scratch, left at zero again) merges them and writes out [B, nq * dh].
-constexpr int kFusedAttnThreads = 128;
+constexpr int kFusedAttnThreads = 256;
+constexpr int kFusedAttnWarps = kFusedAttnThreads / 32;
 constexpr int kFusedAttnMaxSplit = 32;
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
@@ -249,10 +266,10 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 
 template <int DH>
-__global__ void __launch_bounds__(kFusedAttnThreads) rope_attn_kernel(
+__global__ void __launch_bounds__(kFusedAttnThreads, 2) rope_attn_kernel(
     const __half *qkv, const __half *qn, const __half *kn, const __half *cos_t, const __half *sin_t, const long long *pos,
     __half *k_cache, __half *v_cache, float *part, int *counters, __half *out, int nq, int nkv, int S, float scale,
-    float eps) {
+    float eps, int nsplit, int npair) {
   constexpr int TP = 8192 / DH;        // rows per tile: 16 KB of V, a little more of K
   constexpr int KP = 2 * DH + 16;      // K row pitch in shared memory (bytes)
   constexpr int VP = 2 * DH;
@@ -263,13 +280,28 @@ __global__ void __launch_bounds__(kFusedAttnThreads) rope_attn_kernel(
   uint8_t *ks = smem;                           // [2][TP][KP]
   uint8_t *vs = smem + 2 * TP * KP;             // [2][TP][VP]
   float *qs = reinterpret_cast<float *>(vs + 2 * TP * VP);  // [group][DH]
+  constexpr int W = kFusedAttnWarps;
+  constexpr int PR = DH + 4;  // a partial: max, sum, two unused, then the DH weighted values (16-byte aligned)
   __shared__ int s_last;
 
   pdl_launch_dependents();
   pdl_wait();
-  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, nsplit = gridDim.x;
-  const int group = nq / nkv;
+  // CTA -> (sequence, KV head, split).  The grid has one CTA per SM (or one per (sequence, KV
+  // head) when those outnumber the SMs); CTAs beyond the work linger (see below).
+  const int pair = static_cast<int>(blockIdx.x) / nsplit, split = static_cast<int>(blockIdx.x) - pair * nsplit;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (pair >= npair) {
+    linger(4000);
+    return;
+  }
+  const int kvh = pair % nkv, b = pair / nkv;
+  const int group = nq / nkv;
+  // Warp -> (query head, slice of the rows): hp heads are served at a time, by nsl warps each;
+  // the warps of a head take every nsl-th block of 32 rows and are merged in shared memory.
+  const int hp = min(group, W), nsl = max(1, W / hp);
+  const int slice = warp / hp, head0 = warp - slice * hp;
+  const bool active = slice < nsl;
+  float *mrg = qs + group * DH;  // [W][2][PR]: partials of the slices above 0
   // Loads that do not depend on the position go first, so that they share a round trip with it:
   // the raw values of this warp's first query head and the norm weights.
   const __half *row = qkv + 1ll * b * (nq + 2 * nkv) * DH;
@@ -281,13 +313,16 @@ __global__ void __launch_bounds__(kFusedAttnThreads) rope_attn_kernel(
       x1[t] = __half2float(src[lane + 32 * t + HALF]);
     }
   };
-  if (warp < group) load_row(row + 1ll * (kvh * group + warp) * DH, qx0, qx1);
+  if (slice == 0) load_row(row + 1ll * (kvh * group + head0) * DH, qx0, qx1);
   if (qn) load_row(qn, qw0, qw1);
   const long long p_new = *pos;
   const int n = static_cast<int>(p_new) + 1;
-  const int chunk = (((n + nsplit - 1) / nsplit) + 31) & ~31;
+  const int chunk = (n + nsplit - 1) / nsplit;
   const int used = (n + chunk - 1) / chunk;
-  if (split >= used) return;
+  if (split >= used) {
+    linger(4000);
+    return;
+  }
   const int p0 = split * chunk, p1 = min(n, p0 + chunk);
   const int ntile = (p1 - p0 + TP - 1) / TP;
   const __half *kb = k_cache + (1ll * b * nkv + kvh) * S * DH;
@@ -337,9 +372,9 @@ __global__ void __launch_bounds__(kFusedAttnThreads) rope_attn_kernel(
       o1[t] = __half2float(__float2half_rn(y1 * c1[t] + y0 * s1[t]));
     }
   };
-  for (int hq = warp; hq < group; hq += 4) {
+  for (int hq = head0; slice == 0 && hq < group; hq += hp) {
     float o0[HALF / 32], o1[HALF / 32];
-    if (hq != warp) load_row(row + 1ll * (kvh * group + hq) * DH, qx0, qx1);
+    if (hq != head0) load_row(row + 1ll * (kvh * group + hq) * DH, qx0, qx1);
     norm_rope(qx0, qx1, qn != nullptr, qw0, qw1, o0, o1);
 #pragma unroll
     for (int t = 0; t < HALF / 32; ++t) {
@@ -347,11 +382,11 @@ __global__ void __launch_bounds__(kFusedAttnThreads) rope_attn_kernel(
       qs[hq * DH + lane + 32 * t + HALF] = o1[t] * scale;
     }
   }
-  // The new row is the last row of the last tile of its CTA.  Warp 3 (key) and warp 2 (value)
-  // keep it in registers, write it to the cache now and into the tile when that tile is current.
+  // The new row is the last row of the last tile of its CTA.  The last warp (key) and the one
+  // before it (value) keep it in registers, write it to the cache now and into the tile when that tile is current.
   float knew0[HALF / 32], knew1[HALF / 32];
   __half vnew[DPL];
-  if (owns_new && warp == 3) {
+  if (owns_new && warp == W - 1) {
     float kx0[HALF / 32], kx1[HALF / 32], kw0[HALF / 32], kw1[HALF / 32];
     load_row(row + 1ll * (nq + kvh) * DH, kx0, kx1);
     if (kn) load_row(kn, kw0, kw1);
@@ -363,7 +398,7 @@ __global__ void __launch_bounds__(kFusedAttnThreads) rope_attn_kernel(
       kd[lane + 32 * t + HALF] = __float2half_rn(knew1[t]);
     }
   }
-  if (owns_new && warp == 2) {
+  if (owns_new && warp == W - 2) {
     const __half *src = row + 1ll * (nq + nkv + kvh) * DH;
     __half *vd = v_cache + ((1ll * b * nkv + kvh) * S + p_new) * DH;
 #pragma unroll
@@ -374,9 +409,9 @@ __global__ void __launch_bounds__(kFusedAttnThreads) rope_attn_kernel(
   }
 
   // ---- 2./3. tiles
-  float m_run[4], l_run[4], acc[4][DPL];  // up to 4 heads per warp (group <= 16)
+  float m_run[2], l_run[2], acc[2][DPL];  // up to 2 heads per warp (group <= 16)
 #pragma unroll
-  for (int h = 0; h < 4; ++h) {
+  for (int h = 0; h < 2; ++h) {
     m_run[h] = -INFINITY;
     l_run[h] = 0.f;
 #pragma unroll
@@ -387,7 +422,7 @@ __global__ void __launch_bounds__(kFusedAttnThreads) rope_attn_kernel(
     const int r0 = p0 + t * TP, rows = min(TP, p1 - r0), st = t & 1;
     if (owns_new && t == ntile - 1) {
       const int rr = static_cast<int>(p_new) - r0;
-      if (warp == 3) {
+      if (warp == W - 1) {
         __half *sd = reinterpret_cast<__half *>(ks + (st * TP + rr) * KP);
 #pragma unroll
         for (int u = 0; u < HALF / 32; ++u) {
@@ -395,7 +430,7 @@ __global__ void __launch_bounds__(kFusedAttnThreads) rope_attn_kernel(
           sd[lane + 32 * u + HALF] = __float2half_rn(knew1[u]);
         }
       }
-      if (warp == 2) {
+      if (warp == W - 2) {
         __half *sd = reinterpret_cast<__half *>(vs + (st * TP + rr) * VP);
 #pragma unroll
         for (int j = 0; j < DPL; ++j) sd[lane + 32 * j] = vnew[j];
@@ -403,11 +438,11 @@ __global__ void __launch_bounds__(kFusedAttnThreads) rope_attn_kernel(
     }
     __syncthreads();  // tile t (and, the first time, qs; the last time, the new row) visible to all warps
 #pragma unroll
-    for (int h = 0; h < 4; ++h) {
-      const int hq = warp + 4 * h;
-      if (hq >= group) break;
+    for (int h = 0; h < 2; ++h) {
+      const int hq = head0 + hp * h;
+      if (!active || hq >= group) break;
       const float4 *q4 = reinterpret_cast<const float4 *>(qs + hq * DH);
-      for (int rb = 0; rb < rows; rb += 32) {
+      for (int rb = 32 * slice; rb < rows; rb += 32 * nsl) {
         const int r = rb + lane;
         float s = -INFINITY;
         if (r < rows) {
@@ -455,19 +490,51 @@ __global__ void __launch_bounds__(kFusedAttnThreads) rope_attn_kernel(
     if (t + 2 < ntile) load_tile(t + 2);
   }
 
-  // ---- 4. partials, merge by the last CTA of this (b, kvh)
+  // ---- 4. partials: slices above 0 hand theirs to slice 0 through shared memory, slice 0 writes
+  // the CTA's partial; merge by the last CTA of this (b, kvh)
 #pragma unroll
-  for (int h = 0; h < 4; ++h) {
-    const int hq = warp + 4 * h;
-    if (hq >= group) break;
-    const float l = warp_sum(l_run[h]);
-    float *dst = part + ((1ll * b * nq + kvh * group + hq) * nsplit + split) * (DH + 2);
-    if (lane == 0) {
-      dst[0] = m_run[h];
-      dst[1] = l;
+  for (int h = 0; h < 2; ++h) l_run[h] = warp_sum(l_run[h]);
+  if (active && slice > 0) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (head0 + hp * h >= group) break;
+      float *dst = mrg + (warp * 2 + h) * PR;
+      if (lane == 0) {
+        dst[0] = m_run[h];
+        dst[1] = l_run[h];
+      }
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) dst[4 + lane * DPL + j] = acc[h][j];
     }
+  }
+  __syncthreads();
+  if (slice == 0) {
 #pragma unroll
-    for (int j = 0; j < DPL; ++j) dst[2 + lane * DPL + j] = acc[h][j];
+    for (int h = 0; h < 2; ++h) {
+      const int hq = head0 + hp * h;
+      if (hq >= group) break;
+      float m = m_run[h];
+      for (int sl = 1; sl < nsl; ++sl) m = fmaxf(m, mrg[((sl * hp + head0) * 2 + h) * PR]);
+      // (a slice that saw no row has max -inf and weight 0; slice 0 of a CTA with work always has rows)
+      const float w0 = __expf(m_run[h] - m);
+      float l = l_run[h] * w0;
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) acc[h][j] *= w0;
+      for (int sl = 1; sl < nsl; ++sl) {
+        const float *src = mrg + ((sl * hp + head0) * 2 + h) * PR;
+        const float ws = __expf(src[0] - m);
+        l += src[1] * ws;
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) acc[h][j] += ws * src[4 + lane * DPL + j];
+      }
+      float *dst = part + ((1ll * b * nq + kvh * group + hq) * nsplit + split) * PR;
+      if (lane == 0) {
+        dst[0] = m;
+        dst[1] = l;
+      }
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) dst[4 + lane * DPL + j] = acc[h][j];
+    }
   }
   __threadfence();
   __syncthreads();
@@ -479,24 +546,50 @@ __global__ void __launch_bounds__(kFusedAttnThreads) rope_attn_kernel(
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  for (int hq = warp; hq < group; hq += 4) {
+  // The merging CTA reads `used` partials per head out of L2.  All loads of a batch of splits are
+  // issued before any is used (the first batch together with the (max, sum) pairs): two or three
+  // round trips per head instead of one per split.
+  constexpr int BATCH = 64 / DPL;  // splits per batch: 64 value registers per lane
+  for (int hq = warp; hq < group; hq += W) {
     const int head = kvh * group + hq;
-    const float *src = part + (1ll * b * nq + head) * nsplit * (DH + 2);
-    // lane s holds split s's (max, sum); nsplit <= 32
-    const float ms = lane < used ? __ldcg(src + lane * (DH + 2)) : -INFINITY;
-    const float ls = lane < used ? __ldcg(src + lane * (DH + 2) + 1) : 0.f;
-    const float m = warp_max(ms);
-    const float w = lane < used ? __expf(ms - m) : 0.f;
-    const float l = warp_sum(ls * w);
+    const float *src = part + (1ll * b * nq + head) * nsplit * PR;
     float a[DPL];
 #pragma unroll
     for (int j = 0; j < DPL; ++j) a[j] = 0.f;
-#pragma unroll 4
-    for (int sidx = 0; sidx < used; ++sidx) {
-      const float ws = __shfl_sync(0xffffffffu, w, sidx);
-      const float *pv = src + sidx * (DH + 2) + 2 + lane * DPL;
+    float m = 0.f, l = 0.f, w = 0.f;
+    for (int s0 = 0; s0 < used; s0 += BATCH) {
+      float v[BATCH][DPL];
 #pragma unroll
-      for (int j = 0; j < DPL; ++j) a[j] += ws * __ldcg(pv + j);
+      for (int q = 0; q < BATCH; ++q) {
+        if (s0 + q < used) {
+          const float *pv = src + (s0 + q) * PR + 4 + lane * DPL;
+          if (DPL == 4) {
+            const float4 t = __ldcg(reinterpret_cast<const float4 *>(pv));
+            v[q][0] = t.x; v[q][1] = t.y; v[q][2] = t.z; v[q][3] = t.w;
+          } else {
+#pragma unroll
+            for (int j = 0; j < DPL; j += 2) {
+              const float2 t = __ldcg(reinterpret_cast<const float2 *>(pv + j));
+              v[q][j] = t.x; v[q][j + 1] = t.y;
+            }
+          }
+        }
+      }
+      if (s0 == 0) {  // lane s holds split s's (max, sum); nsplit <= 32
+        const float ms = lane < used ? __ldcg(src + lane * PR) : -INFINITY;
+        const float ls = lane < used ? __ldcg(src + lane * PR + 1) : 0.f;
+        m = warp_max(ms);
+        w = lane < used ? __expf(ms - m) : 0.f;
+        l = warp_sum(ls * w);
+      }
+#pragma unroll
+      for (int q = 0; q < BATCH; ++q) {
+        if (s0 + q < used) {
+          const float ws = __shfl_sync(0xffffffffu, w, s0 + q);
+#pragma unroll
+          for (int j = 0; j < DPL; ++j) a[j] += ws * v[q][j];
+        }
+      }
     }
     __half *o = out + (1ll * b * nq + head) * DH + lane * DPL;
     const float inv = 1.f / l;
@@ -505,33 +598,55 @@ __global__ void __launch_bounds__(kFusedAttnThreads) rope_attn_kernel(
   }
 }
 
+// `slot`: the kernel sits between two GEMVs of a decode step: it reserves kSlotSmem of (unused)
+// shared memory so that no SM takes two of its CTAs (see pin_slot).
 template <typename... Args>
-int launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, bool pdl, cudaStream_t stream, Args... args) {
+int launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, bool slot, bool pdl, cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
-  cfg.dynamicSmemBytes = 0;
+  cfg.dynamicSmemBytes = slot ? kSlotSmem : 0;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (slot) RDQ_CUDA(pin_slot(reinterpret_cast<const void *>(kernel), kSlotSmem));
   RDQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, args...));
   return RDQ_OK;
 }
 
 }  // namespace
 
+// An SM cannot change its shared-memory carve-out while a CTA is resident, and the kernels of a
+// decode step overlap on every SM: all of them ask for the largest carve-out, like the GEMV.
+// `smem` is the dynamic shared memory the kernel will be launched with.  Once per kernel, device
+// and size.
+cudaError_t pin_slot(const void *fn, int smem) {
+  static std::mutex mu;
+  static std::vector<std::pair<std::pair<const void *, int>, int>> done;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  for (const auto &d : done)
+    if (d.first.first == fn && d.first.second == dev && d.second >= smem) return cudaSuccess;
+  e = cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  if (e == cudaSuccess && smem > 48 * 1024) e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e == cudaSuccess) done.push_back({{fn, dev}, smem});
+  return e;
+}
+
 int launch_add_rmsnorm(__half *x, const __half *delta, const __half *w, __half *out, int B, int H, float eps, bool pdl,
                        cudaStream_t stream) {
-  return launch_pdl(add_rmsnorm_kernel, dim3(B), dim3(256), pdl, stream, x, delta, w, out, H, eps);
+  return launch_pdl(add_rmsnorm_kernel, dim3(std::max(B, sm_count())), dim3(256), true, pdl, stream, x, delta, w, out, B, H, eps);
 }
 
 int launch_qk_rope_cache(const __half *qkv, const __half *qn, const __half *kn, const __half *cos_t, const __half *sin_t,
                          const long long *pos, __half *q_out, __half *k_cache, __half *v_cache, int B, int nq, int nkv,
                          int dh, int S, float eps, bool pdl, cudaStream_t stream) {
-  return launch_pdl(qk_rope_cache_kernel, dim3(nq + 2 * nkv, B), dim3(dh / 2), pdl, stream, qkv, qn, kn, cos_t, sin_t, pos,
+  return launch_pdl(qk_rope_cache_kernel, dim3(nq + 2 * nkv, B), dim3(dh / 2), false, pdl, stream, qkv, qn, kn, cos_t, sin_t, pos,
                     q_out, k_cache, v_cache, nq, nkv, dh, S, eps);
 }
 
@@ -541,23 +656,23 @@ int launch_attn_decode(const __half *q, const __half *k_cache, const __half *v_c
                        __half *out, int B, int nq, int nkv, int dh, int S, float scale, bool pdl, cudaStream_t stream) {
   const int chunk = attn_chunk();
   const int nsplit = (S + chunk - 1) / chunk;
-  int rc = launch_pdl(attn_split_kernel, dim3(nsplit, nkv, B), dim3(kAttnWarps * 32), pdl, stream, q, k_cache, v_cache, pos,
+  int rc = launch_pdl(attn_split_kernel, dim3(nsplit, nkv, B), dim3(kAttnWarps * 32), false, pdl, stream, q, k_cache, v_cache, pos,
                       scratch, nq, nkv, dh, S, chunk, scale);
   if (rc != RDQ_OK) return rc;
-  return launch_pdl(attn_combine_kernel, dim3(nq, B), dim3(dh), pdl, stream, static_cast<const float *>(scratch), out, nq, dh,
+  return launch_pdl(attn_combine_kernel, dim3(nq, B), dim3(dh), false, pdl, stream, static_cast<const float *>(scratch), out, nq, dh,
                     nsplit);
 }
 
+// Splits of the cache rows per (sequence, KV head): as many as give every SM one CTA.
 int rope_attn_splits(int B, int nkv, int S) {
-  int nsplit = std::min(kFusedAttnMaxSplit, std::max(1, (S + 127) / 128));
-  while (nsplit > 1 && 1ll * nsplit * nkv * B > 2ll * sm_count()) --nsplit;
-  return nsplit;
+  (void)S;
+  return std::min(kFusedAttnMaxSplit, std::max(1, sm_count() / std::max(1, B * nkv)));
 }
 
 size_t rope_attn_scratch_bytes(int B, int nq, int nkv, int dh, int S) {
   // counters first (4-byte ints, rounded up to 256 bytes), then the partials
   const size_t cnt = (static_cast<size_t>(B) * nkv * sizeof(int) + 255) & ~static_cast<size_t>(255);
-  return cnt + sizeof(float) * static_cast<size_t>(B) * nq * rope_attn_splits(B, nkv, S) * (dh + 2);
+  return cnt + sizeof(float) * static_cast<size_t>(B) * nq * rope_attn_splits(B, nkv, S) * (dh + 4);
 }
 
 int launch_rope_attn(const __half *qkv, const __half *qn, const __half *kn, const __half *cos_t, const __half *sin_t,
@@ -569,15 +684,11 @@ int launch_rope_attn(const __half *qkv, const __half *qn, const __half *kn, cons
   float *part = reinterpret_cast<float *>(static_cast<uint8_t *>(scratch) + cnt);
   const int group = nq / nkv;
   const int tp = 8192 / dh;
-  const int smem = 2 * tp * (2 * dh + 16) + 2 * tp * 2 * dh + group * dh * 4;
-  static std::atomic<int> smem_set[3];  // per head_dim variant: largest dynamic shared memory asked for so far
-  auto launch = [&](auto kernel, int variant) -> int {
-    if (smem_set[variant].load() < smem) {
-      RDQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      smem_set[variant].store(smem);
-    }
+  const int smem = 2 * tp * (2 * dh + 16) + 2 * tp * 2 * dh + group * dh * 4 + kFusedAttnWarps * 2 * (dh + 4) * 4;
+  auto launch = [&](auto kernel) -> int {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(nsplit, nkv, B);
+    // one CTA per SM while the (sequence, KV head) pairs fit: like the GEMVs around it
+    cfg.gridDim = dim3(std::max(sm_count(), nsplit * nkv * B));
     cfg.blockDim = dim3(kFusedAttnThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -586,14 +697,15 @@ int launch_rope_attn(const __half *qkv, const __half *qn, const __half *kn, cons
     attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    RDQ_CUDA(pin_slot(reinterpret_cast<const void *>(kernel), smem));
     RDQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, qkv, qn, kn, cos_t, sin_t, pos, k_cache, v_cache, part, counters, out, nq, nkv, S,
-                                scale, eps));
+                                scale, eps, nsplit, nkv * B));
     return RDQ_OK;
   };
   switch (dh) {
-    case 64: return launch(rope_attn_kernel<64>, 0);
-    case 128: return launch(rope_attn_kernel<128>, 1);
-    case 256: return launch(rope_attn_kernel<256>, 2);
+    case 64: return launch(rope_attn_kernel<64>);
+    case 128: return launch(rope_attn_kernel<128>);
+    case 256: return launch(rope_attn_kernel<256>);
   }
   RDQ_REQUIRE(false, RDQ_E_UNSUPPORTED, "head_dim must be 64, 128 or 256, got %d", dh);
   return RDQ_OK;
@@ -601,8 +713,8 @@ int launch_rope_attn(const __half *qkv, const __half *qn, const __half *kn, cons
 
 int launch_silu_mul(const __half *gu, __half *out, int B, int F, bool pdl, cudaStream_t stream) {
   const long long total = 1ll * B * (F / 8);
-  const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 4ll * sm_count()));
-  return launch_pdl(silu_mul_kernel, dim3(blocks), dim3(256), pdl, stream, gu, out, B, F);
+  (void)total;
+  return launch_pdl(silu_mul_kernel, dim3(sm_count()), dim3(256), true, pdl, stream, gu, out, B, F);
 }
 
 }  // namespace rdq

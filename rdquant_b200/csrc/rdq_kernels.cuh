@@ -116,6 +116,11 @@ int launch_add_rmsnorm(__half *x, const __half *delta, const __half *w, __half *
 int launch_qk_rope_cache(const __half *qkv, const __half *qn, const __half *kn, const __half *cos_t, const __half *sin_t,
                          const long long *pos, __half *q_out, __half *k_cache, __half *v_cache, int B, int nq, int nkv,
                          int dh, int S, float eps, bool pdl, cudaStream_t stream);
+// Kernels that sit between two GEMVs of a decode step are launched with one CTA per SM and this
+// much (unused) dynamic shared memory: next to a GEMV's CTA (<= 112 KB + static) an SM then has
+// room for one of their CTAs, not two.
+constexpr int kSlotSmem = 60 * 1024;
+cudaError_t pin_slot(const void *fn, int smem);
 int attn_chunk();
 // q/k norm + rotary + cache write + attention + merge of the splits in one launch
 int rope_attn_splits(int B, int nkv, int S);
