@@ -309,7 +309,7 @@ def prefill_section(device, units, tokens=(512, 2048, 8192), steps: int = 10) ->
 
 
 def decode_section(device, batches=(1, 8), prompt: int = 512, new_tokens: int = 256, cfg=None, rank=0, world=1,
-                   gemv_block_ms=None, peer=True, fuse_prologue=True) -> dict:
+                   gemv_block_ms=None, peer=True, fuse_prologue=True, random_perm=False) -> dict:
     """Whole-model greedy decoding (BASELINE configs[3]): random-init Qwen3-4B-shaped stack, all
     linears mixed-precision, `prompt`-token prefill through the GEMM, then `new_tokens` tokens, one
     CUDA-graph replay per token.  tokens/s = batch * new_tokens / device time of the decode loop."""
@@ -319,13 +319,16 @@ def decode_section(device, batches=(1, 8), prompt: int = 512, new_tokens: int = 
     from rdquant_b200.decoder import QWEN3_4B, MixedDecoder
 
     cfg = cfg or QWEN3_4B
-    out = {"model": cfg.name, "layers": cfg.layers, "prompt_tokens": prompt, "new_tokens": new_tokens, "batch": {}}
+    out = {"model": cfg.name, "layers": cfg.layers, "prompt_tokens": prompt, "new_tokens": new_tokens, "batch": {},
+           "channel_order": "all channels shuffled" if random_perm else
+           "random assignment of channels to formats, grouped by format, original order inside a group (as the "
+           "reference's allocator produces, rdquant/core/allocator.py:210-224)"}
     if world > 1:
         out["parallelism"] = f"column-parallel x{world}, " + ("all-gather fused into the GEMV epilogue (peer stores)"
                                                                if peer else "NCCL all-gather per linear")
     t_build = time.time()
     model = MixedDecoder(cfg, device, max_seq=prompt + new_tokens + 8, batch=batches[0], seed=7, rank=rank, world=world,
-                         peer_gather=peer, fuse_prologue=fuse_prologue)
+                         peer_gather=peer, fuse_prologue=fuse_prologue, random_perm=random_perm)
     torch.cuda.synchronize()
     t_build = time.time() - t_build
     for b in batches:
@@ -583,6 +586,9 @@ def main() -> None:
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM section")
     ap.add_argument("--no-decode", dest="decode", action="store_false", help="skip whole-model decoding")
     ap.add_argument("--decode-batches", default="1,8", help="batch sizes of the whole-model decode section")
+    ap.add_argument("--decode-perm", choices=["grouped", "random"], default="grouped",
+                    help="channel order of the decode section's layers: grouped by format like the reference's "
+                         "allocator output, or fully shuffled (worst case for the output stores)")
     ap.add_argument("--decode-prompt", type=int, default=512, help="prompt tokens of the decode section")
     ap.add_argument("--decode-tokens", type=int, default=256, help="generated tokens of the decode section")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
@@ -763,7 +769,7 @@ def main() -> None:
     if args.decode and m == 1:
         batches = tuple(int(b) for b in args.decode_batches.split(",") if b)
         line["decode"] = decode_section(device, batches=batches, prompt=args.decode_prompt, new_tokens=args.decode_tokens,
-                                        gemv_block_ms=ms / steps,
+                                        gemv_block_ms=ms / steps, random_perm=args.decode_perm == "random",
                                         fuse_prologue={"all": True, "none": False}.get(args.prologue, args.prologue))
         line["config"]["decode_tokens_per_s"] = line["decode"]["batch"][str(batches[0])]["tokens_per_s"]
     if not args.no_cpu_baseline:

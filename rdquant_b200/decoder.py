@@ -79,11 +79,12 @@ class MixedDecoder:
 
     def __init__(self, cfg: DecoderConfig, device, max_seq: int, batch: int, seed: int = 0, rank: int = 0,
                  world: int = 1, group=None, use_pdl: bool = True, fused_glue: bool = True, peer_gather: bool = True,
-                 fuse_prologue=True, fused_attention: bool = True) -> None:
+                 fuse_prologue=True, fused_attention: bool = True, random_perm: bool = False) -> None:
         self.cfg, self.device, self.max_seq, self.batch = cfg, torch.device(device), max_seq, batch
         self.rank, self.world, self.group = rank, world, group
         self.use_pdl, self.fused_glue, self.fuse_prologue = use_pdl, fused_glue, fuse_prologue
         self.fused_attention = fused_attention and cfg.head_dim in (64, 128, 256)
+        self.random_perm = random_perm
         self.arena = None
         if world > 1 and peer_gather:
             from rdquant_b200.parallel import PeerArena
@@ -145,6 +146,20 @@ class MixedDecoder:
         }
 
     # ---- construction
+    def _permutation(self, n, sp, gen):
+        """Channel order of a layer: a random assignment of the channels to the formats, grouped by
+        format with the original order kept inside a group -- what the reference's allocator
+        produces (rdquant/core/allocator.py:210-224).  ``random_perm=True`` shuffles all channels
+        instead (the worst case for the locality of the output stores)."""
+        if self.random_perm:
+            return torch.randperm(n, generator=gen, device=self.device)
+        shuffled = torch.randperm(n, generator=gen, device=self.device)
+        parts, off = [], 0
+        for fmt in ("NVFP4", "FP8", "FP16"):
+            parts.append(shuffled[off:off + sp[fmt]].sort().values)
+            off += sp[fmt]
+        return torch.cat(parts)
+
     def _linear(self, shapes, gen, use_pdl):
         cfg = self.cfg
         parts = []
@@ -152,8 +167,8 @@ class MixedDecoder:
             w = (torch.randn(n, k, generator=gen, device=self.device, dtype=torch.float32) * 0.02)
             idx = torch.randperm(n, generator=gen, device=self.device)[: n // 100]
             w[idx] *= 8
-            perm = torch.randperm(n, generator=gen, device=self.device)
             sp = _splits(n, cfg)
+            perm = self._permutation(n, sp, gen)
             parts.append((quantize_weight_packed(w.half(), perm, sp), sp))
             self.linear_bytes += packed_weight_bytes(sp, k)
             del w
