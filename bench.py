@@ -318,6 +318,10 @@ def decode_section(device, batches=(1, 8), prompt: int = 512, new_tokens: int = 
 
     from rdquant_b200.decoder import QWEN3_4B, MixedDecoder
 
+    if isinstance(cfg, str):
+        from rdquant_b200.decoder import LLAMA3_70B
+
+        cfg = {"qwen3-4b": QWEN3_4B, "llama3-70b": LLAMA3_70B}[cfg]
     cfg = cfg or QWEN3_4B
     out = {"model": cfg.name, "layers": cfg.layers, "prompt_tokens": prompt, "new_tokens": new_tokens, "batch": {},
            "channel_order": "all channels shuffled" if random_perm else
@@ -564,7 +568,8 @@ def run_sharded(args, device, rank: int, world: int) -> None:
     }
     del graph, ggraph  # graphs that captured collectives must go before the process group does
     if args.decode:
-        line["decode"] = decode_section(device, batches=(1,), rank=rank, world=world, peer=peer)
+        line["decode"] = decode_section(device, batches=(1,), prompt=args.decode_prompt, new_tokens=args.decode_tokens,
+                                        cfg=args.decode_model, rank=rank, world=world, peer=peer)
     if rank == 0:
         print(json.dumps(line), flush=True)
 
@@ -584,11 +589,14 @@ def main() -> None:
     ap.add_argument("--prologue", choices=["all", "norm", "act", "none"], default="all",
                     help="whole-model decode: which of add+RMSNorm / SiLU x mul run inside the consuming GEMV")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM section")
+    ap.add_argument("--prefill-tokens", default="512,2048,8192", help="token counts of the prefill GEMM section")
     ap.add_argument("--no-decode", dest="decode", action="store_false", help="skip whole-model decoding")
     ap.add_argument("--decode-batches", default="1,8", help="batch sizes of the whole-model decode section")
     ap.add_argument("--decode-perm", choices=["grouped", "random"], default="grouped",
                     help="channel order of the decode section's layers: grouped by format like the reference's "
                          "allocator output, or fully shuffled (worst case for the output stores)")
+    ap.add_argument("--decode-model", choices=["qwen3-4b", "llama3-70b"], default="qwen3-4b",
+                    help="shape of the whole-model decode section (BASELINE configs 4 / 5)")
     ap.add_argument("--decode-prompt", type=int, default=512, help="prompt tokens of the decode section")
     ap.add_argument("--decode-tokens", type=int, default=256, help="generated tokens of the decode section")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
@@ -762,14 +770,16 @@ def main() -> None:
         "clocks": clocks,
     }
     if not args.no_prefill and m == 1:
-        line["prefill"] = prefill_section(device, layers)
+        line["prefill"] = prefill_section(device, layers, tokens=tuple(int(t) for t in args.prefill_tokens.split(",") if t))
     for l in layers:
         l["fds"] = l["fds"][:1]
     torch.cuda.empty_cache()
     if args.decode and m == 1:
         batches = tuple(int(b) for b in args.decode_batches.split(",") if b)
         line["decode"] = decode_section(device, batches=batches, prompt=args.decode_prompt, new_tokens=args.decode_tokens,
-                                        gemv_block_ms=ms / steps, random_perm=args.decode_perm == "random",
+                                        cfg=args.decode_model,
+                                        gemv_block_ms=ms / steps if args.decode_model == "qwen3-4b" else None,
+                                        random_perm=args.decode_perm == "random",
                                         fuse_prologue={"all": True, "none": False}.get(args.prologue, args.prologue))
         line["config"]["decode_tokens_per_s"] = line["decode"]["batch"][str(batches[0])]["tokens_per_s"]
     if not args.no_cpu_baseline:
