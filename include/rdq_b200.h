@@ -414,6 +414,18 @@ int rdq_silu_mul(const void *gate_up, void *out, int B, int F, int flags,
  * (benchmarks/bench_e2e.py:103-155).
  */
 int rdq_stage_copy(void *dst, const void *src, size_t bytes, void *stream);
+/*
+ * The same copy, followed by a completion signal the host can poll instead of
+ * synchronising the stream: after a system-scope fence behind all of its
+ * stores the kernel writes the number of rdq_stage_copy_signal launches
+ * completed on `state` so far (1, 2, ...) to *flag.
+ *   state: two device ints, zero before the first call, owned by the library
+ *          between calls (CTAs done, launches completed)
+ *   flag:  one int in pinned host memory (read with a volatile / acquire load)
+ * A host thread that sees *flag == k may read what the k-th launch copied.
+ */
+int rdq_stage_copy_signal(void *dst, const void *src, size_t bytes,
+                          int32_t *state, int32_t *flag, void *stream);
 
 #ifdef __cplusplus
 }

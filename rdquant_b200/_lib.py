@@ -134,6 +134,8 @@ def _bind(lib: ctypes.CDLL) -> None:
     lib.rdq_silu_mul.argtypes = [vp, vp, i32, i32, i32, vp]
     lib.rdq_stage_copy.restype = i32
     lib.rdq_stage_copy.argtypes = [vp, vp, ctypes.c_size_t, vp]
+    lib.rdq_stage_copy_signal.restype = i32
+    lib.rdq_stage_copy_signal.argtypes = [vp, vp, ctypes.c_size_t, vp, vp, vp]
 
 
 EXPORTS = [
@@ -160,6 +162,7 @@ EXPORTS = [
     "rdq_quantize_nvfp4",
     "rdq_quantize_fp8",
     "rdq_stage_copy",
+    "rdq_stage_copy_signal",
     "rdq_add_rmsnorm",
     "rdq_qk_rope_cache",
     "rdq_attn_decode_scratch_size",

@@ -462,7 +462,14 @@ int rdq_silu_mul(const void *gate_up, void *out, int B, int F, int flags, void *
 int rdq_stage_copy(void *dst, const void *src, size_t bytes, void *stream) {
   RDQ_REQUIRE(bytes == 0 || (dst != nullptr && src != nullptr), RDQ_E_INVALID, "dst and src must not be null");
   RDQ_REQUIRE(aligned16(dst) && aligned16(src), RDQ_E_INVALID, "dst and src must be 16-byte aligned");
-  return launch_stage_copy(dst, src, bytes, static_cast<cudaStream_t>(stream));
+  return launch_stage_copy(dst, src, bytes, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int rdq_stage_copy_signal(void *dst, const void *src, size_t bytes, int32_t *state, int32_t *flag, void *stream) {
+  RDQ_REQUIRE(bytes == 0 || (dst != nullptr && src != nullptr), RDQ_E_INVALID, "dst and src must not be null");
+  RDQ_REQUIRE(aligned16(dst) && aligned16(src), RDQ_E_INVALID, "dst and src must be 16-byte aligned");
+  RDQ_REQUIRE(state != nullptr && flag != nullptr, RDQ_E_INVALID, "state and flag must not be null");
+  return launch_stage_copy(dst, src, bytes, state, flag, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

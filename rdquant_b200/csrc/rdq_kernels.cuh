@@ -108,7 +108,7 @@ void gemm_set_test_timeout(bool on);
 size_t gemm_workspace_bytes(int M, int N, int K);
 
 // staging copy by kernel (rdq_stage.cu)
-int launch_stage_copy(void *dst, const void *src, size_t bytes, cudaStream_t stream);
+int launch_stage_copy(void *dst, const void *src, size_t bytes, int *state, int *flag, cudaStream_t stream);
 
 // decode-step glue (rdq_glue.cu)
 int launch_add_rmsnorm(__half *x, const __half *delta, const __half *w, __half *out, int B, int H, float eps, bool pdl,

@@ -8,6 +8,7 @@ no dequantised FP16 copy of the weights is kept, so ``use_dense_prefill`` costs 
 from __future__ import annotations
 
 import json
+import time
 import os
 from typing import Optional
 
@@ -144,12 +145,14 @@ class GraphedDecodeStep:
     buffer to the device, the fused GEMV (programmatic dependent launch between layers) and
     the copy of the result to a pinned host buffer.  ``run()`` replays it and waits for the
     results, so a caller holding host-side activations pays one launch per step instead of
-    three calls per layer.  (The reference's end-to-end timings rely on CUDA-graph capture
+    three calls per layer.  The wait is a poll of a word in pinned host memory that the last
+    copy kernel writes behind its data (``poll=False``: a stream synchronisation).  (The reference's end-to-end timings rely on CUDA-graph capture
     of the decode step the same way, benchmarks/bench_e2e.py:103-155.)
     """
 
-    def __init__(self, modules, m: int = 1, use_pdl: bool = True) -> None:
+    def __init__(self, modules, m: int = 1, use_pdl: bool = True, poll: bool = True) -> None:
         self.modules = list(modules)
+        self.poll = poll
         dev = self.modules[0].inv_perm.device
         # one pinned staging buffer each way: a single copy node per direction in the graph
         ks = [m * mod.K for mod in self.modules]
@@ -183,10 +186,18 @@ class GraphedDecodeStep:
             cuda.stage_copy(self._x_all_dev, self._x_all_host)
             for i, mod in enumerate(self.modules):
                 cuda.mixed_gemv(self._x_dev[i], mod._fd(), biases[i], flags, out=self._y_dev[i])
-            cuda.stage_copy(self._y_all_host, self._y_all_dev)
+            if self.poll:
+                cuda.stage_copy(self._y_all_host, self._y_all_dev, self._done_state, self._done_flag)
+            else:
+                cuda.stage_copy(self._y_all_host, self._y_all_dev)
 
+        self._done_state = torch.zeros(2, dtype=torch.int32, device=dev)
+        self._done_flag = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._done_view = self._done_flag.numpy()
+        self._launches = 0
         with torch.cuda.stream(self._stream):
             body()  # first calls outside capture (library set-up, lazy module loading)
+            self._launches += 1
             self._stream.synchronize()
             with torch.cuda.graph(self._graph, stream=self._stream):
                 body()
@@ -194,7 +205,19 @@ class GraphedDecodeStep:
     def run(self):
         """Replay: ``x_host`` -> device -> linears -> ``y_host``; returns ``y_host`` when complete."""
         self._graph.replay()  # on the caller's current stream
-        torch.cuda.current_stream(self._x_all_dev.device).synchronize()
+        self._launches += 1
+        if self.poll:
+            # the copy kernel writes the launch count behind its data (system-scope release)
+            view, want = self._done_view, self._launches
+            deadline = None
+            while int(view[0]) != want:
+                if deadline is None:
+                    deadline = time.monotonic() + 10.0
+                elif time.monotonic() > deadline:
+                    torch.cuda.current_stream(self._x_all_dev.device).synchronize()
+                    raise RuntimeError(f"decode step did not signal completion (flag {int(view[0])}, expected {want})")
+        else:
+            torch.cuda.current_stream(self._x_all_dev.device).synchronize()
         return self.y_host
 
 

@@ -417,10 +417,15 @@ def quantize_fp8_packed(w: torch.Tensor, want_sqerr: bool = False) -> dict:
     return out
 
 
-def stage_copy(dst: torch.Tensor, src: torch.Tensor) -> None:
+def stage_copy(dst: torch.Tensor, src: torch.Tensor, state: Optional[torch.Tensor] = None,
+               flag: Optional[torch.Tensor] = None) -> None:
     """Copy ``src`` into ``dst`` (same byte size, contiguous) with a small kernel on the current
     stream.  One side lives on the GPU, the other may be pinned host memory: inside a CUDA
-    graph this replaces a memcpy node and its fixed latency."""
+    graph this replaces a memcpy node and its fixed latency.
+
+    With ``state`` (two zeroed CUDA int32) and ``flag`` (one pinned host int32) the kernel then
+    writes the number of such copies completed so far to ``flag``: the host may poll it
+    instead of synchronising the stream."""
     dev_t = dst if dst.is_cuda else src
     if not dev_t.is_cuda:
         raise RuntimeError("stage_copy needs one CUDA tensor")
@@ -430,8 +435,17 @@ def stage_copy(dst: torch.Tensor, src: torch.Tensor) -> None:
     nbytes = dst.numel() * dst.element_size()
     if nbytes != src.numel() * src.element_size():
         raise RuntimeError("stage_copy: size mismatch")
+    if (state is None) != (flag is None):
+        raise RuntimeError("stage_copy: state and flag go together")
     with _on_device(dev_t.device):
-        _lib.check(_lib.lib().rdq_stage_copy(_ptr(dst), _ptr(src), nbytes, _stream(dev_t.device)), "rdq_stage_copy")
+        if flag is None:
+            _lib.check(_lib.lib().rdq_stage_copy(_ptr(dst), _ptr(src), nbytes, _stream(dev_t.device)), "rdq_stage_copy")
+        else:
+            if not (state.is_cuda and state.dtype == torch.int32 and state.numel() >= 2 and flag.is_pinned()
+                    and flag.dtype == torch.int32):
+                raise RuntimeError("stage_copy: state must be 2 CUDA int32, flag a pinned host int32")
+            _lib.check(_lib.lib().rdq_stage_copy_signal(_ptr(dst), _ptr(src), nbytes, _ptr(state), _ptr(flag),
+                                                        _stream(dev_t.device)), "rdq_stage_copy_signal")
 
 
 # ---- decode-step glue (rdq_glue.cu): thin wrappers, all tensors preallocated by the caller

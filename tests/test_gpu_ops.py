@@ -62,18 +62,42 @@ def test_fused_mixed_linear_module(layers):
         mod(torch.randn(1, k).half())  # CPU input: no host path
 
 
-def test_graphed_decode_step(layers):
+@pytest.mark.parametrize("poll", [True, False])
+def test_graphed_decode_step(layers, poll):
+    """Host buffers in, host buffers out, one graph replay; completion seen by polling the word
+    the last copy kernel writes behind its data, or by a stream synchronisation."""
     from rdquant_b200.inference import GraphedDecodeStep
 
     mods = []
     for name in ("mixed_384x256", "alloc_512x256"):
         layer, splits, k = golden_layer_torch(layers[name])
         mods.append(FusedMixedLinear.from_layer_data(layer, splits, k, "cuda"))
-    step = GraphedDecodeStep(mods, m=2)
-    for call in range(2):
+    step = GraphedDecodeStep(mods, m=2, poll=poll)
+    for call in range(5):
         xs = [torch.randn(2, mod.K).half() for mod in mods]
         for xh, x in zip(step.x_host, xs):
             xh.copy_(x)
         ys = step.run()
         for mod, x, y in zip(mods, xs, ys):
             assert torch.equal(y, mod(x.cuda()).cpu()), call
+    if poll:
+        assert int(step._done_flag[0]) == 6  # the warm-up call and five replays
+
+
+def test_stage_copy_signal():
+    """The signalled copy: odd sizes, device -> pinned host, the flag counts the launches."""
+    from rdquant_b200 import rdquant_cuda
+
+    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32).pin_memory()
+    for launch, nbytes in enumerate((16, 61440, 4096 * 37 + 5, 3), start=1):
+        src = torch.randint(0, 255, (nbytes,), dtype=torch.uint8, device="cuda")
+        dst = torch.zeros(nbytes, dtype=torch.uint8).pin_memory()
+        rdquant_cuda.stage_copy(dst, src, state, flag)
+        torch.cuda.synchronize()
+        assert int(flag[0]) == launch and torch.equal(dst, src.cpu())
+        back = torch.zeros_like(src)
+        rdquant_cuda.stage_copy(back, dst)  # pinned host -> device, no signal
+        torch.cuda.synchronize()
+        assert torch.equal(back, src)
+    assert state.tolist() == [0, 4]
