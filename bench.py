@@ -765,8 +765,9 @@ def main() -> None:
                 "d2h_bytes_per_step": sum(2 * m * l["n"] for l in layers), "steps": e2e_steps,
                 "ms_per_step": 1e3 * te / e2e_steps,
                 "api": "inference.GraphedDecodeStep.run(): pinned host x -> device (staging kernel reading the pinned "
-                       "buffer), fused GEMVs, y -> pinned host (staging kernel) as one CUDA-graph replay, synchronised "
-                       "every step; weight copies rotate as in the device-only measurement"},
+                       "buffer), fused GEMVs, y -> pinned host (staging kernel) as one CUDA-graph replay; every step the "
+                       "host waits for the completion word the last kernel writes to pinned memory behind its data; "
+                       "weight copies rotate as in the device-only measurement"},
         "clocks": clocks,
     }
     if not args.no_prefill and m == 1:
