@@ -138,3 +138,24 @@ def test_rope_attn_decode_single_launch(b, nq, nkv, dh, norm, s, pos_v):
     _close(out, ref.reshape(b, nq * dh))
     nbytes = (b * nkv * 4 + 255) // 256 * 256
     assert int(scratch.view(torch.int32)[: nbytes // 4].abs().sum()) == 0
+
+
+def test_rope_attn_decode_refuses_what_it_cannot_run():
+    f16 = dict(dtype=torch.float16, device="cuda")
+    pos = torch.zeros(1, dtype=torch.long, device="cuda")
+
+    def call(nq, nkv, dh, s=64, qkv_cols=None):
+        qkv = torch.zeros(1, qkv_cols or (nq + 2 * nkv) * dh, **f16)
+        cos = torch.zeros(s, dh, **f16)
+        kc = torch.zeros(1, nkv, s, dh, **f16)
+        out = torch.zeros(1, nq * dh, **f16)
+        scratch = torch.zeros(1 << 16, dtype=torch.float32, device="cuda")
+        rc.rope_attn_decode(qkv, None, None, cos, cos, pos, kc, kc.clone(), scratch, out, nq, 1.0, 1e-6)
+
+    call(4, 2, 64)  # fine
+    with pytest.raises(RuntimeError, match="head_dim"):
+        call(4, 2, 96)
+    with pytest.raises(RuntimeError, match="query heads per KV head"):
+        call(34, 2, 64)
+    with pytest.raises(RuntimeError):
+        call(4, 2, 64, qkv_cols=100)
