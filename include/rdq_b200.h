@@ -373,7 +373,8 @@ int rdq_quantize_fp8(const void *w, int w_is_f32, int n, int K,
  *                       to finish merges the splits.  Same rounding points as
  *                       the two separate calls (q and the new k are rounded to
  *                       f16 before use).  scratch:
- *                       rdq_rope_attn_decode_scratch_size bytes, 16-byte
+ *                       rdq_rope_attn_decode_scratch_size bytes (enough for
+ *                       every batch up to the B it is asked for), 16-byte
  *                       aligned, ZERO before the first call (it starts with the
  *                       arrival counters, which every call leaves at zero); not
  *                       to be shared by calls that may overlap.

@@ -670,9 +670,12 @@ int rope_attn_splits(int B, int nkv, int S) {
 }
 
 size_t rope_attn_scratch_bytes(int B, int nq, int nkv, int dh, int S) {
-  // counters first (4-byte ints, rounded up to 256 bytes), then the partials
+  // counters first (4-byte ints, rounded up to 256 bytes), then the partials.  Sized for every
+  // batch up to B (fewer sequences get more splits each), so one buffer serves smaller batches.
   const size_t cnt = (static_cast<size_t>(B) * nkv * sizeof(int) + 255) & ~static_cast<size_t>(255);
-  return cnt + sizeof(float) * static_cast<size_t>(B) * nq * rope_attn_splits(B, nkv, S) * (dh + 4);
+  size_t rows = 0;
+  for (int b = 1; b <= B; ++b) rows = std::max(rows, static_cast<size_t>(b) * rope_attn_splits(b, nkv, S));
+  return cnt + sizeof(float) * rows * nq * (dh + 4);
 }
 
 int launch_rope_attn(const __half *qkv, const __half *qn, const __half *kn, const __half *cos_t, const __half *sin_t,
