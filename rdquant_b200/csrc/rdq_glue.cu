@@ -240,7 +240,7 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __half *gu, __half 
 // ---- q/k RMSNorm + rotary embedding + KV-cache write + attention of the new token over the
 // cache + merge of the splits, in one launch.
 // One CTA per SM, 128 threads: CTA c is (sequence, KV head) c / nsplit and split c % nsplit, with
-// nsplit = SMs / (sequences x KV heads) (at most 32); it serves the `group` query heads of its KV
+// nsplit = SMs / (sequences x KV heads) (at most 16); it serves the `group` query heads of its KV
 // head over the cache rows [split * chunk, (split + 1) * chunk) with chunk = the n = *pos + 1
 // rows divided by nsplit, rounded up to 32; warp w takes the heads w, w + 4, ...
 //   1. every CTA normalises and rotates its query heads into shared memory (FP16-rounded like the
@@ -254,7 +254,7 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __half *gu, __half 
 //      (counter in scratch, left at zero again) merges them and writes out [B, nq * dh].
 constexpr int kFusedAttnThreads = 256;
 constexpr int kFusedAttnWarps = kFusedAttnThreads / 32;
-constexpr int kFusedAttnMaxSplit = 32;
+constexpr int kFusedAttnMaxSplit = 16;  // one batch of merge loads at head_dim <= 128
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
