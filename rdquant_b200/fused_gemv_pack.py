@@ -1,8 +1,10 @@
 """Build the device buffers of the fused mixed-precision kernels from checkpoint tensors.
 
 Same entry points as the reference (rdquant/fused_gemv_pack.py:37-57, :275-354).  The
-kernels consume the checkpoint's row-major tensors as they are, so "packing" is a device
-copy plus the derived output permutation and the stream kernel's scratch; no re-tiling.
+prefill GEMM, the dequantiser and the any-shape GEMV consume the checkpoint's row-major
+tensors as they are; the decode GEMV reads a re-tiled copy of them (taken from the checkpoint
+when it carries one, else produced here), so "packing" is a device copy, that copy, the
+derived output permutation and the decode kernel's scratch.
 """
 from __future__ import annotations
 
@@ -29,7 +31,7 @@ def fused_gemv_available() -> bool:
 
 
 def choose_parallel_k(num_tiles: int, k: int) -> int:
-    """Kept for signature parity (rdquant/fused_gemv_pack.py:60-63); the stream kernel
+    """Kept for signature parity (rdquant/fused_gemv_pack.py:60-63); the decode kernel
     balances k inside the launch, so there is no caller-visible split factor."""
     return 1
 
@@ -74,7 +76,7 @@ def pack_for_fused_gemv(layer_data: dict, splits: dict, k: int, device,
     """Device buffers for ``rdquant_cuda.mixed_gemv`` / ``mixed_gemm``.
 
     Accepts any split (single-format layers, an FP16 group, groups below 128 channels);
-    shapes the stream kernel does not take run on the any-shape kernel.  Returns ``None``
+    shapes without a tiled layout run on the any-shape kernel.  Returns ``None``
     only when the kernels are unavailable, like the reference
     (rdquant/fused_gemv_pack.py:289-290).
 
