@@ -4,13 +4,15 @@ reference's harness is benchmarks/bench_e2e.py:103-155 over a HuggingFace model)
 
 q/k/v and gate/up are packed as one layer each (they read the same input).  In the prefill pass
 everything that is not a linear layer -- embedding lookup, RMSNorm, rotary embedding, attention,
-SiLU x mul, residual adds -- is plain PyTorch.  A decode step uses the glue kernels of
-csrc/rdq_glue.cu instead (residual add + RMSNorm, q/k norm + rotary + cache write, single-token
-attention, SiLU x mul: 9 launches per block, all chained by programmatic dependent launch with the
-GEMVs), or, with ``fused_glue=False``, the same PyTorch operators as the prefill; the embedding
-lookup, the FP16 lm_head and the arg-max are PyTorch in both.  A decode step has static
-shapes (the KV cache is allocated for the whole run, the current position lives in a device
-tensor), so it is captured once in a CUDA graph and replayed per token.
+SiLU x mul, residual adds -- is plain PyTorch.  A decode step uses the kernels of csrc/rdq_glue.cu
+instead, chained by programmatic dependent launch with the GEMVs: on one GPU a block is five
+launches -- q+k+v GEMV with the add + RMSNorm as its activation prologue, one launch for q/k norm +
+rotary + cache write + attention, o GEMV, gate+up GEMV (add + RMSNorm prologue), down GEMV (SiLU x
+mul prologue); where a prologue does not apply (larger batches, several GPUs) the same steps run
+as kernels of their own.  ``fused_glue=False`` runs the PyTorch operators of the prefill instead;
+the embedding lookup, the FP16 lm_head and the arg-max are PyTorch in both.  A decode step has
+static shapes (the KV cache is allocated for the whole run, the current position lives in a
+device tensor), so it is captured once in a CUDA graph and replayed per token.
 
 With ``world > 1`` every linear is column-parallel: each rank streams its rows and the full
 activation is rebuilt on every rank -- by stores into every GPU's gather buffer from the GEMV's
