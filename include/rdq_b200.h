@@ -353,6 +353,13 @@ int rdq_quantize_fp8(const void *w, int w_is_f32, int n, int K,
  * reference leaves this code to the HuggingFace model around its modules
  * (module boundary rdquant/inference.py:689-708; harness
  * benchmarks/bench_e2e.py:103-155).  All tensors f16 unless stated, row-major.
+ * rdq_add_rmsnorm, rdq_rope_attn_decode, rdq_silu_mul (and rdq_peer_gather,
+ * rdq_stage_copy) launch one CTA per SM, each sized so that an SM takes one of
+ * them beside a GEMV's CTA and no second one, and CTAs without work stay
+ * resident for a few microseconds: the tiled GEMV is fastest while every SM
+ * holds exactly one CTA of each launch of the chain, and a kernel of a few CTAs
+ * between two GEMVs breaks that (CTAs of the next GEMV pile up on the SMs that
+ * free a slot first).
  *   rdq_add_rmsnorm     x[B,H] += delta[B,H] (delta may be NULL: no add);
  *                       out[B,H] = f16(x * rsqrt(mean(x^2) + eps)) * weight[H]
  *   rdq_qk_rope_cache   qkv[B, (nq + 2 nkv) * dh] (q heads, k heads, v heads):
