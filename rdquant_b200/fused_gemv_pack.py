@@ -72,13 +72,17 @@ def validate_layer_data(layer_data: dict, splits: dict, k: int) -> tuple[int, in
 
 
 def pack_for_fused_gemv(layer_data: dict, splits: dict, k: int, device,
-                        honor_global_scale: bool = False, tiled: bool = True) -> Optional[dict]:
+                        honor_global_scale: bool = False, tiled: bool = True, row_major: bool = True) -> Optional[dict]:
     """Device buffers for ``rdquant_cuda.mixed_gemv`` / ``mixed_gemm``.
 
     Accepts any split (single-format layers, an FP16 group, groups below 128 channels);
     shapes without a tiled layout run on the any-shape kernel.  Returns ``None``
     only when the kernels are unavailable, like the reference
     (rdquant/fused_gemv_pack.py:289-290).
+
+    ``row_major=False`` keeps only the re-tiled copy on the device when the shape has one
+    (half the weight memory): the decode GEMV is unaffected, more than 16 rows then run as
+    16-row panels of it instead of the tensor-core GEMM, and the dequantiser has no input.
 
     The NVFP4 block scales of a checkpoint are absolute, so the kernel's global-scale
     argument is 1.0 unless ``honor_global_scale`` asks for the stored value
@@ -129,6 +133,11 @@ def pack_for_fused_gemv(layer_data: dict, splits: dict, k: int, device,
             fd["tiled_from_checkpoint"] = True
         else:
             fd["w_tiled"] = rdquant_cuda.repack_tiled(fd)
+    fd["row_major"] = True
+    if not row_major and fd["w_tiled"] is not None:
+        for key in ("w_fp4_q", "w_fp4_scales", "w_fp8_q", "w_fp16"):
+            fd[key] = None
+        fd["row_major"] = False
     return fd
 
 

@@ -128,8 +128,8 @@ class FusedMixedLinear(nn.Module):
         return f"K={self.K}, N={self.N}, nvfp4/fp8/fp16={self.n_nvfp4}/{self.n_fp8}/{self.n_fp16}"
 
     @classmethod
-    def from_layer_data(cls, layer_data: dict, splits: dict, k: int, device) -> "FusedMixedLinear":
-        fd = pack_for_fused_gemv(layer_data, dict(splits), k, device)
+    def from_layer_data(cls, layer_data: dict, splits: dict, k: int, device, row_major: bool = True) -> "FusedMixedLinear":
+        fd = pack_for_fused_gemv(layer_data, dict(splits), k, device, row_major=row_major)
         if fd is None:
             raise RuntimeError("rdquant_b200 kernels unavailable: build librdq_b200.so and run on a CUDA device")
         bias = layer_data.get("bias")
@@ -234,12 +234,12 @@ def _set_module(model: nn.Module, name: str, new_module: nn.Module) -> None:
     setattr(parent, parts[-1], new_module)
 
 
-def replace_quantized_layers(model: nn.Module, layer_configs: dict, tensors: dict, device) -> None:
+def replace_quantized_layers(model: nn.Module, layer_configs: dict, tensors: dict, device, row_major: bool = True) -> None:
     """Install a :class:`FusedMixedLinear` for every layer of ``layer_configs``."""
     for layer_name, lconf in layer_configs.items():
         pre = layer_name + "."
         layer_data = {k[len(pre):]: v for k, v in tensors.items() if k.startswith(pre)}
-        mod = FusedMixedLinear.from_layer_data(layer_data, lconf["splits"], lconf["in_features"], device)
+        mod = FusedMixedLinear.from_layer_data(layer_data, lconf["splits"], lconf["in_features"], device, row_major=row_major)
         _set_module(model, layer_name, mod)
 
 
@@ -250,12 +250,16 @@ def load_for_inference(
     use_marlin: bool = True,
     use_fused_gemv: bool = True,
     use_dense_prefill: bool = True,
+    decode_only: bool = False,
 ) -> nn.Module:
     """Load a packed checkpoint into a HuggingFace model whose quantised linears are
     :class:`FusedMixedLinear`.
 
     ``use_marlin`` / ``use_fused_gemv`` / ``use_dense_prefill`` are accepted for signature
     parity (rdquant/inference.py:715-722); the fused kernels serve decode and prefill alike.
+    ``decode_only=True`` keeps only the decode kernel's tiled copy of every layer on the device
+    (half the weight memory; the reference's dense prefill instead adds an FP16 copy,
+    rdquant/inference.py:742-744): prompts then run as 16-row panels of the decode kernel.
     """
     from safetensors import safe_open
     from transformers import AutoConfig, AutoModelForCausalLM
@@ -286,7 +290,7 @@ def load_for_inference(
     from rdquant_b200.integrations.hf_export import read_tiled_layout
 
     tensors.update(read_tiled_layout(checkpoint_dir))
-    replace_quantized_layers(model, layer_configs, tensors, target)
+    replace_quantized_layers(model, layer_configs, tensors, target, row_major=not decode_only)
 
     quant_layers = tuple(name + "." for name in layer_configs)
     for pname, param in model.named_parameters():

@@ -217,6 +217,8 @@ def mixed_gemv(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None, f
         if VALIDATE:
             check_status(fd)
         return y
+    if not fd.get("row_major", True):
+        raise RuntimeError("this layer was packed without its row-major tensors: only the tiled decode kernel can run it")
     with _on_device(x.device):
         rc = _lib.lib().rdq_gemv_mixed(
             _ptr(x), m, _ptr(fd.get("w_fp4_q")), _ptr(fd.get("w_fp4_scales")), float(fd.get("w_fp4_global_scale", 1.0)),
@@ -295,6 +297,8 @@ def mixed_gemm(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None,
         raise RuntimeError("out must be a contiguous float16 [M, N] tensor")
     if m == 0 or n == 0:
         return y
+    if not fd.get("row_major", True):
+        raise RuntimeError("this layer was packed without its row-major tensors: the prefill GEMM cannot run it")
     with _on_device(x.device):
         # scratch for problems with few tiles (the library then splits the k range); the
         # per-device buffer only grows and is reused by later calls on the same stream order
@@ -321,10 +325,11 @@ def mixed_linear(x: torch.Tensor, fd: dict, bias: Optional[torch.Tensor] = None,
     """GEMV for M <= 16, GEMM above."""
     if x.shape[0] <= MAX_GEMV_M:
         return mixed_gemv(x, fd, bias, flags, out=out)
-    if fd["k"] % 64 == 0:
+    if fd["k"] % 64 == 0 and fd.get("row_major", True):
         return mixed_gemm(x, fd, bias, out=out)
-    # the tensor-core GEMM tiles K in blocks of 64; other K run the decode kernel over 16-row
-    # panels (the reference's dense prefill takes any K, rdquant/inference.py:679-687)
+    # the tensor-core GEMM tiles K in blocks of 64 and reads the row-major tensors; other K, and
+    # layers packed without them, run the decode kernel over 16-row panels (the reference's
+    # dense prefill takes any K, rdquant/inference.py:679-687)
     n = fd["n_fp4"] + fd["n_fp8"] + fd["n_fp16"]
     y = out if out is not None else torch.empty(x.shape[0], n, dtype=torch.float16, device=x.device)
     for r0 in range(0, x.shape[0], MAX_GEMV_M):

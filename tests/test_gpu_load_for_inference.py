@@ -137,3 +137,44 @@ def test_tiled_layout_in_checkpoint_is_used_as_is(tmp_path):
     assert torch.equal(again.get_submodule(names[0])._fd()["w_tiled"], plain.get_submodule(names[0])._fd()["w_tiled"])
     save_file(tiled, os.path.join(tmp_path, hf_export.TILED_FILE), metadata={"layout": "something else"})
     assert hf_export.read_tiled_layout(str(tmp_path)) == {}
+
+
+@pytest.mark.gpu
+def test_decode_only_load_keeps_one_copy_of_the_weights(tmp_path):
+    """decode_only=True drops the row-major tensors (the tiled copy alone stays on the device):
+    decode-sized inputs give the same bits as the full load, longer inputs run as 16-row panels
+    of the decode kernel and agree with the tensor-core GEMM within the FP32-sum tolerance."""
+    from rdquant_b200 import rdquant_cuda
+    from rdquant_b200.inference import load_for_inference
+
+    names = write_checkpoint(str(tmp_path))
+    full = load_for_inference(str(tmp_path), device="cuda")
+    lean = load_for_inference(str(tmp_path), device="cuda", decode_only=True)
+
+    def weight_bytes(model):
+        total = 0
+        for n in names:
+            fd = model.get_submodule(n)._fd()
+            total += sum(fd[k].numel() * fd[k].element_size() for k in ("w_fp4_q", "w_fp4_scales", "w_fp8_q", "w_fp16", "w_tiled")
+                         if fd.get(k) is not None)
+        return total
+
+    for n in names:
+        fd = lean.get_submodule(n)._fd()
+        assert fd["row_major"] is False and fd["w_tiled"] is not None
+        assert all(fd.get(k) is None for k in ("w_fp4_q", "w_fp4_scales", "w_fp8_q", "w_fp16"))
+    assert weight_bytes(lean) < 0.55 * weight_bytes(full)
+
+    gen = torch.Generator().manual_seed(4)
+    ids = torch.randint(0, 512, (1, 7), generator=gen).cuda()
+    with torch.no_grad():
+        assert torch.equal(full(input_ids=ids).logits, lean(input_ids=ids).logits)
+        ids = torch.randint(0, 512, (1, 45), generator=gen).cuda()
+        a, b = full(input_ids=ids).logits.float(), lean(input_ids=ids).logits.float()
+    assert float((a - b).abs().max() / a.abs().max()) < 5e-3
+    fd = lean.get_submodule(names[0])._fd()
+    x = torch.zeros(32, fd["k"], dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError, match="row-major"):
+        rdquant_cuda.mixed_gemm(x, fd)
+    with pytest.raises(RuntimeError, match="row-major"):
+        rdquant_cuda.mixed_gemv(x[:1], fd, None, 1)  # forced any-shape kernel
