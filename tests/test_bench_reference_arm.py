@@ -24,3 +24,18 @@ def test_reference_arm_prints_the_contract_line():
     e2e = line["e2e"]
     assert e2e["value"] == line["value"] and e2e["unit"] == line["unit"]
     assert e2e["h2d_bytes_per_step"] == 0 and e2e["d2h_bytes_per_step"] == 0
+
+
+def test_own_arm_refuses_to_run_without_a_gpu():
+    """There is no CPU path to time: without a CUDA device the repository's own arm stops with
+    a message instead of printing a number."""
+    import pytest
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present: the own arm would run the benchmark")
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--steps", "1", "--warmup", "1", "--no-cpu-baseline"],
+                          cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert proc.returncode != 0
+    assert not [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
+    assert "CUDA" in (proc.stderr + proc.stdout)
